@@ -1,0 +1,302 @@
+"""Benchmark of the KV-cache compression hot path: quantize+pack then unpack+dequantize.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+A step is one pass over a whole synthetic KV cache of the Qwen2.5-3B shape
+(36 layers x 2 KV heads x 8192 tokens x head_dim 128, fp16, 4 of 128 channels
+per head scaled x10): every layer's keys are quantised to 4 bits and values to
+2 bits (TurboQuantV3, residual_window=0, protected_layers=0), then every layer
+is dequantised back into fp16 tensors.  With N > 1 (torchrun, one rank per GPU)
+each rank processes its own cache of that size -- the (layer, KV head) units of
+an N-times larger batch -- with no collective on the data path (weak scaling).
+
+One JSON line is printed by rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "turboquant-pytorch_b200"))
+
+import torch  # noqa: E402
+
+LAYERS, KV_HEADS, SEQ, HEAD_DIM = 36, 2, 8192, 128
+KEY_BITS, VALUE_BITS = 4, 2
+METRIC = "KV vectors/s quantize+dequantize"
+WORKLOAD = ("configs[1]: Qwen2.5-3B-shaped KV cache, 36 layers x 2 KV heads x seq 8192 x head_dim 128, batch 1, fp16, "
+            "N(0,1) with 4/128 outlier channels x10, TurboQuantV3 K4/V2, residual_window=0, protected_layers=0")
+
+
+def algorithmic_bytes_per_vector(bits: int, elem_bytes: int = 2) -> int:
+    """D*sizeof(elem) + packed row + fp16 norm, for quantise and for dequantise to the cache dtype."""
+    ipb = 8 // bits
+    return HEAD_DIM * elem_bytes + (HEAD_DIM + ipb - 1) // ipb + 2
+
+
+def synthetic_layer(device, seed: int, dtype=torch.float16):
+    g = torch.Generator(device=device).manual_seed(seed)
+    x = torch.randn(1, KV_HEADS, SEQ, HEAD_DIM, generator=g, device=device, dtype=torch.float32)
+    gc = torch.Generator(device="cpu").manual_seed(seed)
+    for h in range(KV_HEADS):
+        ch = torch.randperm(HEAD_DIM, generator=gc)[:4].to(device)
+        x[:, h, :, ch] *= 10.0
+    return x.to(dtype)
+
+
+class ClockSampler:
+    """Polls NVML (read only) for SM clock and throttle reasons while the timed region runs."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def cpu_reference_pass(n_layers: int, threads: int):
+    """Oracle port of the reference's CPU path on `n_layers` layers; returns (vectors, seconds)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import tq_oracle as O
+    torch.set_num_threads(threads)
+    cache = {}
+    vectors, seconds = 0, 0.0
+    for layer in range(n_layers):
+        codec = O.V3Oracle(HEAD_DIM, key_bits=KEY_BITS, value_bits=VALUE_BITS, residual_window=0, layer_idx=layer,
+                           n_layers=LAYERS, protected_layers=0, codebook_cache=cache)
+        keys = O.synthetic_kv((1, KV_HEADS, SEQ, HEAD_DIM), torch.float16, 20000 + layer)
+        vals = O.synthetic_kv((1, KV_HEADS, SEQ, HEAD_DIM), torch.float16, 25000 + layer)
+        t0 = time.perf_counter()
+        ck, cv = codec.compress_kv(keys, vals)
+        codec.decompress_kv(ck, cv)
+        seconds += time.perf_counter() - t0
+        vectors += 2 * KV_HEADS * SEQ
+    return vectors, seconds
+
+
+def run_reference(args, rank: int):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    sample_layers = 4
+    for _ in range(args.warmup):
+        cpu_reference_pass(1, threads)
+    vec, sec = 0, 0.0
+    for _ in range(args.steps):
+        v, s = cpu_reference_pass(sample_layers, threads)
+        vec += v
+        sec += s
+    value = vec / sec
+    sample = f"{sample_layers} of {LAYERS} layers per step (K4 + V2, compress_kv + decompress_kv), {args.steps} steps"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "vectors/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sec / max(args.steps, 1),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "arm": "CPU restatement of the reference (oracle/tq_oracle.py), torch CPU ops"},
+        "cpu_baseline": {"value": value, "unit": "vectors/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "vectors/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="layers per rank (smaller values are for profiling only)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import turboquant as tq
+    from turboquant import _native, batched
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device for --impl b200"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _native.lib()
+    n_layers = args.layers
+
+    codecs = [tq.TurboQuantV3(HEAD_DIM, key_bits=KEY_BITS, value_bits=VALUE_BITS, residual_window=0, layer_idx=l,
+                              n_layers=LAYERS, protected_layers=0, device=dev) for l in range(n_layers)]
+    keys = [synthetic_layer(dev, 20000 + 100000 * rank + l) for l in range(n_layers)]
+    vals = [synthetic_layer(dev, 25000 + 100000 * rank + l) for l in range(n_layers)]
+    vectors_per_step = 2 * n_layers * KV_HEADS * SEQ
+    bytes_q = n_layers * KV_HEADS * SEQ * (algorithmic_bytes_per_vector(KEY_BITS) + algorithmic_bytes_per_vector(VALUE_BITS))
+    bytes_d = bytes_q
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # larger than the 126 MB L2
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one_step(ev=None):
+        flush.zero_()
+        if ev:
+            ev[0].record()
+        packed = batched.compress_kv_layers(codecs, keys, vals)
+        if ev:
+            ev[1].record()
+        flush.zero_()
+        if ev:
+            ev[2].record()
+        outs = batched.decompress_kv_layers(codecs, packed)
+        if ev:
+            ev[3].record()
+        return packed, outs
+
+    for _ in range(args.warmup):
+        one_step()
+    events = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    barrier()
+    launches0 = lib.tq_launch_count()
+    with ClockSampler(local_rank) as clocks:
+        for s in range(args.steps):
+            one_step(events[s])
+        barrier()
+    launches = lib.tq_launch_count() - launches0
+    t_q = sum(e[0].elapsed_time(e[1]) for e in events) * 1e-3
+    t_d = sum(e[2].elapsed_time(e[3]) for e in events) * 1e-3
+    total = torch.tensor([t_q + t_d, t_q, t_d], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total, op=dist.ReduceOp.MAX)
+    t_all, t_q, t_d = total.tolist()
+
+    # ---- end to end through the public API from pinned host memory ------------
+    h_keys = [k.cpu().pin_memory() for k in keys]
+    h_vals = [v.cpu().pin_memory() for v in vals]
+    h_out_k = [torch.empty_like(k).pin_memory() for k in h_keys]
+    h_out_v = [torch.empty_like(v).pin_memory() for v in h_vals]
+    e2e_steps = max(1, min(args.steps, 5))
+
+    def e2e_step():
+        dk = [k.to(dev, non_blocking=True) for k in h_keys]
+        dv = [v.to(dev, non_blocking=True) for v in h_vals]
+        packed = batched.compress_kv_layers(codecs, dk, dv)
+        outs = batched.decompress_kv_layers(codecs, packed)
+        for l, (rk, rv) in enumerate(outs):
+            h_out_k[l].copy_(rk, non_blocking=True)
+            h_out_v[l].copy_(rv, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    t_e2e = torch.tensor([e0.elapsed_time(e1) * 1e-3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
+    t_e2e = float(t_e2e.item())
+    io_bytes = sum(k.numel() * k.element_size() for k in h_keys) * 2
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+    ach_q = bytes_q * args.steps / t_q / 1e9
+    ach_d = bytes_d * args.steps / t_d / 1e9
+    dominant = ("quantize", ach_q, t_q) if t_q >= t_d else ("dequantize", ach_d, t_d)
+    out = {
+        "metric": METRIC, "value": world * vectors_per_step * args.steps / t_all, "unit": "vectors/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_all / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers_per_gpu": n_layers, "units_per_gpu": n_layers * KV_HEADS,
+                   "vectors_per_step_per_gpu": vectors_per_step,
+                   "l2": "a 256 MiB buffer is overwritten before each phase (outside the event-timed intervals); "
+                         "inputs and outputs (302 MB each) exceed the 126 MB L2",
+                   "timing": "CUDA events around the quantize phase and the dequantize phase of every step, summed; max over ranks"},
+        "roofline": {"bound": "hbm", "kernel": dominant[0], "achieved": dominant[1], "peak": peak_gbs, "unit": "GB/s",
+                     "frac": dominant[1] / peak_gbs, "traffic": None, "peak_source": peak_src,
+                     "phases": {"quantize": {"GB/s": ach_q, "frac": ach_q / peak_gbs, "ms": 1e3 * t_q / args.steps,
+                                             "algorithmic_bytes": bytes_q},
+                                "dequantize": {"GB/s": ach_d, "frac": ach_d / peak_gbs, "ms": 1e3 * t_d / args.steps,
+                                               "algorithmic_bytes": bytes_d}}},
+        "e2e": {"value": world * vectors_per_step * e2e_steps / t_e2e, "unit": "vectors/s",
+                "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes, "steps": e2e_steps,
+                "ms_per_step": 1e3 * t_e2e / e2e_steps,
+                "what": "pinned host fp16 K,V -> device -> compress_kv_layers -> decompress_kv_layers -> pinned host fp16 K,V"},
+        "gpu_launches": int(launches),
+        "clocks": clocks.summary(),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        v, s = cpu_reference_pass(1, threads)            # warm-up: codebooks, thread pool
+        layers = max(1, min(LAYERS, int(12.0 / max(s, 1e-3))))
+        v, s = cpu_reference_pass(layers, threads)
+        out["cpu_baseline"] = {"value": v / s, "unit": "vectors/s", "cores": threads, "kind": "port",
+                               "sample": f"{layers} of {LAYERS} layers of the same workload, one pass, {s:.1f} s"}
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

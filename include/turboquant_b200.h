@@ -1,0 +1,222 @@
+/*
+ * turboquant_b200.h -- C ABI of libturboquant_b200.so
+ *
+ * B200 (sm_100a) kernels for the TurboQuant KV-cache compression hot path.
+ * Every entry point takes plain pointers and sizes.  Device pointers are marked
+ * [dev], host pointers [host].  The library never allocates, frees or retains
+ * caller memory, never synchronises the device, and enqueues all work on the
+ * stream that is passed in (a cudaStream_t, given as void*).  The caller makes
+ * the right device current before the call.
+ *
+ * Each function returns TQ_OK (0) or a negative TQ_E* code; tq_strerror() turns
+ * a code into text.  No function throws or aborts.
+ *
+ * The "Replaces:" lines cite the interface of the reference implementation
+ * (tonbistudio/turboquant-pytorch, file:line in that tree) whose work the entry
+ * point performs.
+ */
+#ifndef TURBOQUANT_B200_H
+#define TURBOQUANT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- codes ------------------------------------------------------------ */
+enum {
+  TQ_OK = 0,
+  TQ_EINVAL = -1,    /* inconsistent sizes / negative counts / bad mode        */
+  TQ_EBITS = -2,     /* bits outside 1..8                                       */
+  TQ_EDIM = -3,      /* head_dim outside 1..256                                 */
+  TQ_ENULL = -4,     /* a required pointer is NULL                              */
+  TQ_EALIGN = -5,    /* pointer or stride breaks the stated alignment           */
+  TQ_EDTYPE = -6,    /* unknown element type code                               */
+  TQ_ELAUNCH = -7,   /* the CUDA runtime refused the launch (see tq_last_cuda_error) */
+  TQ_EWORKSPACE = -8,/* workspace smaller than tq_*_workspace_bytes says        */
+  TQ_ETOOBIG = -9,   /* problem exceeds a fixed capacity of the entry point     */
+  TQ_EDEVICE = -10   /* device is not compute capability 10.x                   */
+};
+
+/* element types of caller tensors */
+enum { TQ_F32 = 0, TQ_F16 = 1, TQ_BF16 = 2 };
+
+/* how indices are laid out in memory */
+enum {
+  TQ_IDX_PACKED = 0, /* 8/bits indices per byte, first index in the high bits,
+                        row = ceil(D / (8/bits)) bytes, zero padded
+                        (turboquant/compressors_v3.py:64-74)                     */
+  TQ_IDX_U8 = 1,     /* one uint8 per index (turboquant/compressors.py:205)     */
+  TQ_IDX_I64 = 2     /* one int64 per index (turboquant/turboquant.py:85)       */
+};
+
+#define TQ_MAX_DIM 256
+#define TQ_CODEBOOK_FLOATS 512
+/* A codebook block is 512 floats on the device: [0,L) centroids ascending,
+ * [256, 256+L-1) decision thresholds, every other slot +inf.  Threshold k is
+ * the largest fp32 y for which fl|y-c_k| <= fl|y-c_(k+1)|, so that
+ * index(y) = #{k : y > threshold_k} equals the first-minimum argmin over
+ * |y - c| evaluated in fp32 (turboquant/compressors_v3.py:60-61).  The identity
+ * holds while ulp(y) is far below the centroid spacing (|y| < 1024 for every
+ * codebook of head_dim 64..256; rotated unit vectors have |y| <= 1); beyond
+ * that fp32 differences tie and the argmin itself stops being monotone.       */
+
+int tq_version(void);
+const char* tq_strerror(int code);
+/* cudaError_t value of the last failed launch on this host thread (0 if none) */
+int tq_last_cuda_error(void);
+/* kernels this library has launched in this process so far (all threads)      */
+int64_t tq_launch_count(void);
+
+/* ---- host-side helpers (no GPU needed) -------------------------------- */
+
+/* Bytes per packed row: ceil(D / (8/bits)).
+ * Replaces: turboquant/compressors_v3.py:64-69 and :112-113.                  */
+int tq_packed_row_bytes(int D, int bits);
+
+/* Fill a 512-float codebook block [host] from L = 2^bits ascending centroids
+ * [host].  Replaces the argmin rule of turboquant/compressors_v3.py:60-61.    */
+int tq_build_codebook(const float* centroids, int bits, float* block512);
+
+/* ---- K0: rotated fp32 values -> indices (the bit-exact gate) ----------- */
+/* y [dev] (n, D) contiguous fp32; out [dev] laid out per idx_mode.
+ * Replaces: turboquant/compressors_v3.py:60-74, turboquant/lloyd_max.py:117-121. */
+int tq_quantize_rotated(const float* y, int64_t n, int D, int bits, const float* codebook,
+                        int idx_mode, void* out, void* stream);
+
+/* ---- K1: norm + rotate + nearest centroid + pack ----------------------- */
+typedef struct {
+  const void* x;          /* [dev] vectors; element (b,h,s,d) at x[b*stride_b + h*stride_h + s*stride_s + d] */
+  int32_t x_dtype;        /* TQ_F32 | TQ_F16 | TQ_BF16                                      */
+  int32_t D;              /* head_dim, 1..256; the last dimension is contiguous             */
+  int32_t bits;           /* 1..8                                                            */
+  int32_t normalize;      /* 1: divide by (||x||+1e-8) and emit norms; 0: quantise x as is  */
+  int64_t B, H, S;        /* vector count = B*H*S                                            */
+  int64_t stride_b, stride_h, stride_s;   /* in elements                                     */
+  const float* rotation_t;/* [dev] Pi^T, (D, D) row-major fp32: y = x @ rotation_t           */
+  const float* codebook;  /* [dev] 512-float block                                           */
+  int32_t idx_mode;       /* TQ_IDX_*                                                        */
+  int32_t reserved;
+  void* idx_out;          /* [dev] (B*H*S, row) contiguous                                   */
+  uint16_t* norms_out;    /* [dev] fp16 bit patterns (B*H*S); may be NULL when normalize==0  */
+} TqQuantizeJob;
+
+/* Runs n_jobs independent jobs [host array].
+ * Replaces: MSECompressor.compress turboquant/compressors_v3.py:45-81 (and the
+ * old-token half of TurboQuantV3.compress_kv :193-207, which it reads through
+ * strides instead of copying); TurboQuantCompressorMSE.compress
+ * turboquant/compressors.py:200-213 (TQ_IDX_U8); TurboQuantMSE.quantize
+ * turboquant/turboquant.py:80-86 (normalize=0, TQ_IDX_I64).                    */
+int tq_quantize(const TqQuantizeJob* jobs, int n_jobs, void* stream);
+
+/* ---- K2: unpack + centroid lookup + inverse rotation + rescale --------- */
+typedef struct {
+  const void* idx;        /* [dev] (B*H*S, row) contiguous, layout idx_mode                  */
+  const uint16_t* norms;  /* [dev] fp16 bit patterns, or NULL for no rescale                 */
+  int32_t idx_mode;
+  int32_t D, bits;
+  int32_t out_dtype;      /* TQ_F32 (drop-in decompress) | TQ_F16 | TQ_BF16 (cache dtype)    */
+  int64_t B, H, S;
+  void* out;              /* [dev] element (b,h,s,d) at out[b*ostride_b + h*ostride_h + s*ostride_s + d] */
+  int64_t ostride_b, ostride_h, ostride_s;
+  const float* rotation;  /* [dev] Pi, (D, D) row-major fp32: x_hat = c[idx] @ rotation      */
+  const float* codebook;  /* [dev] 512-float block                                           */
+} TqDequantizeJob;
+
+/* Replaces: MSECompressor.decompress turboquant/compressors_v3.py:83-105; with a
+ * 16-bit out_dtype and strides into the final (B,H,S_total,D) buffer also the
+ * cast + concatenate of TurboQuantV3.decompress_kv :225-232;
+ * TurboQuantCompressorMSE.decompress turboquant/compressors.py:215-221;
+ * TurboQuantMSE.dequantize turboquant/turboquant.py:88-91 (norms NULL).        */
+int tq_dequantize(const TqDequantizeJob* jobs, int n_jobs, void* stream);
+
+/* ---- generic projection: out = x @ m ---------------------------------- */
+/* x [dev] (n, K) contiguous of x_dtype; m [dev] (K, N) row-major fp32; out (n, N) fp32.
+ * K, N in 1..256.  Replaces: TurboQuantMSE.rotate/unrotate
+ * turboquant/turboquant.py:71-78 and the query projections of
+ * turboquant/compressors.py:147 and turboquant/turboquant.py:185.             */
+int tq_project(const void* x, int x_dtype, int64_t n, int K, const float* m, int N, float* out, void* stream);
+
+/* ---- K3: attention logits straight from packed keys -------------------- */
+typedef struct {
+  const void* q;          /* [dev] (B, Hq, Sq, D) contiguous                                 */
+  int32_t q_dtype;
+  int32_t D, bits;
+  int32_t reserved;
+  int64_t B, Hq, Sq, Hkv, Sk;  /* Hq % Hkv == 0; query head g reads KV head g / (Hq/Hkv)    */
+  const uint8_t* idx_bytes;    /* [dev] (B, Hkv, Sk, row) TQ_IDX_PACKED                      */
+  const uint16_t* norms;       /* [dev] (B, Hkv, Sk) fp16 bits                               */
+  const float* rotation_t;     /* [dev] Pi^T (the key compressor's)                          */
+  const float* codebook;
+  float scale;                 /* logits are multiplied by this (1.0f: raw q.k)              */
+  int32_t reserved2;
+  float* logits;               /* [dev] (B, Hq, Sq, Sk)                                      */
+  float* probs;                /* [dev] softmax over Sk, same shape, or NULL                 */
+  void* workspace;             /* [dev] scratch, 256-byte aligned                            */
+  size_t workspace_bytes;
+} TqScoreJob;
+
+size_t tq_score_workspace_bytes(int64_t B, int64_t Hq, int64_t Sq, int64_t Sk, int D);
+
+/* logits = scale * q . k_hat with k_hat the reconstruction MSECompressor.decompress
+ * would return, computed as norm_s * sum_j (q Pi^T)_j * c[idx_sj] without
+ * materialising keys.
+ * Replaces: compress -> decompress -> matmul of turboquant/validate_v3.py:83-87.  */
+int tq_score_packed(const TqScoreJob* job, void* stream);
+
+/* ---- K4: MSE stage + QJL sign stage ------------------------------------ */
+typedef struct {
+  const void* x; int32_t x_dtype; int32_t D;
+  int32_t bits;           /* width of the MSE stage (already bits-1 of the total budget)     */
+  int32_t normalize;      /* 1: V2 (unit-normalise, rescale k_mse); 0: V1 TurboQuantProd      */
+  int64_t B, H, S; int64_t stride_b, stride_h, stride_s;
+  const float* rotation_t;/* [dev] Pi^T                                                       */
+  const float* rotation;  /* [dev] Pi                                                         */
+  const float* codebook;
+  const float* qjl_t;     /* [dev] S^T, (D, M) row-major fp32: projected = residual @ qjl_t   */
+  int32_t M;              /* QJL projection width, 1..256                                     */
+  int32_t signs_dtype;    /* 0: int8 +-1 with >=0 -> +1; 1: fp32 +-1 with 0 -> +1             */
+  int32_t rnorm_dtype;    /* TQ_F16 | TQ_F32                                                  */
+  int32_t idx_mode;       /* layout of idx_out when it is not NULL                            */
+  uint16_t* k_mse_out;    /* [dev] fp16 (N, D) or NULL                                        */
+  void* idx_out;          /* [dev] or NULL                                                    */
+  void* signs_out;        /* [dev] (N, M)                                                     */
+  void* rnorm_out;        /* [dev] (N)                                                        */
+} TqQjlCompressJob;
+
+/* Replaces: TurboQuantCompressorV2.compress turboquant/compressors.py:83-120;
+ * TurboQuantProd.quantize turboquant/turboquant.py:134-159.                    */
+int tq_qjl_compress(const TqQjlCompressJob* job, void* stream);
+
+/* ---- K5: asymmetric scores from the MSE+QJL representation ------------- */
+typedef struct {
+  const void* q; int32_t q_dtype; int32_t D;
+  int64_t BH, Sq, Sk;          /* q (BH, Sq, D); keys (BH, Sk, ...)                           */
+  const uint16_t* k_mse;       /* [dev] fp16 (BH, Sk, D)                                      */
+  const int8_t* signs;         /* [dev] (BH, Sk, D)                                           */
+  const uint16_t* rnorm;       /* [dev] fp16 (BH, Sk)                                         */
+  const float* qjl_t;          /* [dev] S^T (D, D)                                            */
+  float* scores;               /* [dev] (BH, Sq, Sk)                                          */
+  void* workspace; size_t workspace_bytes;   /* >= tq_qjl_scores_workspace_bytes              */
+} TqQjlScoreJob;
+
+size_t tq_qjl_scores_workspace_bytes(int64_t BH, int64_t Sq, int D);
+
+/* Replaces: TurboQuantCompressorV2.asymmetric_attention_scores
+ * turboquant/compressors.py:122-158.                                           */
+int tq_qjl_scores(const TqQjlScoreJob* job, void* stream);
+
+/* Row-paired estimator <y_n, x_mse_n> + ||r_n|| sqrt(pi/2)/M <S y_n, signs_n>.
+ * y (ny, D) fp32 with ny == n or ny == 1; idx int64 (n, D); signs fp32 (n, M);
+ * rnorm fp32 (n); workspace >= (n + ny) * 256 * 4 bytes.
+ * Replaces: TurboQuantProd.inner_product turboquant/turboquant.py:165-192.     */
+int tq_prod_inner_product(const float* y, int64_t ny, const int64_t* idx, const float* signs, const float* rnorm,
+                          int64_t n, int D, int M, const float* rotation, const float* codebook,
+                          const float* qjl_t, float* out, void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TURBOQUANT_B200_H */

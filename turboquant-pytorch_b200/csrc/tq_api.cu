@@ -1,0 +1,225 @@
+// C ABI of libturboquant_b200.so: argument checking, host helpers, dispatch.
+
+#include <math.h>
+#include <string.h>
+
+#include "tq_internal.h"
+
+namespace {
+
+inline bool bad_dtype(int dt) { return dt != TQ_F32 && dt != TQ_F16 && dt != TQ_BF16; }
+inline bool bad_mode(int m) { return m != TQ_IDX_PACKED && m != TQ_IDX_U8 && m != TQ_IDX_I64; }
+
+// order-preserving map between fp32 values and int32
+inline int32_t f2ord(float f) {
+  int32_t i;
+  memcpy(&i, &f, 4);
+  return i < 0 ? (int32_t)(0x80000000u - (uint32_t)i) : i;
+}
+inline float ord2f(int32_t o) {
+  int32_t i = o < 0 ? (int32_t)(0x80000000u - (uint32_t)o) : o;
+  float f;
+  memcpy(&f, &i, 4);
+  return f;
+}
+
+// fl|y - a| <= fl|y - b| in IEEE single precision (volatile blocks contraction / widening)
+inline bool prefers_lower(float y, float a, float b) {
+  volatile float da = y - a;
+  volatile float db = y - b;
+  return fabsf(da) <= fabsf(db);
+}
+
+int check_common(int D, int bits) {
+  if (bits < 1 || bits > 8) return TQ_EBITS;
+  if (D < 1 || D > TQ_MAX_DIM) return TQ_EDIM;
+  return TQ_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tq_version(void) { return 100; }
+
+const char* tq_strerror(int code) {
+  switch (code) {
+    case TQ_OK: return "ok";
+    case TQ_EINVAL: return "invalid argument (sizes, counts or mode)";
+    case TQ_EBITS: return "bits must be in 1..8";
+    case TQ_EDIM: return "head_dim must be in 1..256";
+    case TQ_ENULL: return "required pointer is NULL";
+    case TQ_EALIGN: return "pointer or stride is misaligned";
+    case TQ_EDTYPE: return "unknown element type";
+    case TQ_ELAUNCH: return "CUDA launch failed";
+    case TQ_EWORKSPACE: return "workspace too small";
+    case TQ_ETOOBIG: return "problem exceeds the capacity of this entry point";
+    case TQ_EDEVICE: return "device is not compute capability 10.x";
+    default: return "unknown error code";
+  }
+}
+
+int tq_last_cuda_error(void) { return tq::last_cuda_error(); }
+
+int64_t tq_launch_count(void) { return (int64_t)tq::launch_count(); }
+
+int tq_packed_row_bytes(int D, int bits) {
+  int rc = check_common(D, bits);
+  if (rc != TQ_OK) return rc;
+  int ipb = 8 / bits;
+  return (D + ipb - 1) / ipb;
+}
+
+int tq_build_codebook(const float* centroids, int bits, float* block) {
+  if (centroids == nullptr || block == nullptr) return TQ_ENULL;
+  if (bits < 1 || bits > 8) return TQ_EBITS;
+  const int L = 1 << bits;
+  for (int i = 0; i + 1 < L; ++i)
+    if (!(centroids[i] < centroids[i + 1])) return TQ_EINVAL;
+  for (int i = 0; i < TQ_CODEBOOK_FLOATS; ++i) block[i] = INFINITY;
+  for (int i = 0; i < L; ++i) block[i] = centroids[i];
+  for (int k = 0; k + 1 < L; ++k) {
+    const float a = centroids[k], b = centroids[k + 1];
+    // prefers_lower is true at y = a and false at y = b, and monotone in between
+    // because rounding is monotone; bisect on the ordered bit patterns.
+    int64_t lo = f2ord(a), hi = f2ord(b);
+    while (hi - lo > 1) {
+      int64_t mid = lo + (hi - lo) / 2;
+      if (prefers_lower(ord2f((int32_t)mid), a, b)) lo = mid; else hi = mid;
+    }
+    block[256 + k] = ord2f((int32_t)lo);
+  }
+  return TQ_OK;
+}
+
+int tq_quantize_rotated(const float* y, int64_t n, int D, int bits, const float* codebook, int idx_mode, void* out,
+                        void* stream) {
+  int rc = check_common(D, bits);
+  if (rc != TQ_OK) return rc;
+  if (n < 0 || bad_mode(idx_mode)) return TQ_EINVAL;
+  if (n == 0) return TQ_OK;
+  if (y == nullptr || codebook == nullptr || out == nullptr) return TQ_ENULL;
+  return tq::simt_quantize_rotated(y, n, D, bits, codebook, idx_mode, out, (cudaStream_t)stream);
+}
+
+int tq_quantize(const TqQuantizeJob* jobs, int n_jobs, void* stream) {
+  if (n_jobs < 0) return TQ_EINVAL;
+  if (n_jobs == 0) return TQ_OK;
+  if (jobs == nullptr) return TQ_ENULL;
+  for (int i = 0; i < n_jobs; ++i) {
+    const TqQuantizeJob& j = jobs[i];
+    int rc = check_common(j.D, j.bits);
+    if (rc != TQ_OK) return rc;
+    if (bad_dtype(j.x_dtype)) return TQ_EDTYPE;
+    if (bad_mode(j.idx_mode) || j.B < 0 || j.H < 0 || j.S < 0) return TQ_EINVAL;
+    if (j.B * j.H * j.S == 0) continue;
+    if (j.x == nullptr || j.rotation_t == nullptr || j.codebook == nullptr || j.idx_out == nullptr) return TQ_ENULL;
+    if (j.normalize && j.norms_out == nullptr) return TQ_ENULL;
+  }
+  for (int i = 0; i < n_jobs; ++i) {
+    int rc = tq::simt_quantize(jobs[i], (cudaStream_t)stream);
+    if (rc != TQ_OK) return rc;
+  }
+  return TQ_OK;
+}
+
+int tq_dequantize(const TqDequantizeJob* jobs, int n_jobs, void* stream) {
+  if (n_jobs < 0) return TQ_EINVAL;
+  if (n_jobs == 0) return TQ_OK;
+  if (jobs == nullptr) return TQ_ENULL;
+  for (int i = 0; i < n_jobs; ++i) {
+    const TqDequantizeJob& j = jobs[i];
+    int rc = check_common(j.D, j.bits);
+    if (rc != TQ_OK) return rc;
+    if (bad_dtype(j.out_dtype)) return TQ_EDTYPE;
+    if (bad_mode(j.idx_mode) || j.B < 0 || j.H < 0 || j.S < 0) return TQ_EINVAL;
+    if (j.B * j.H * j.S == 0) continue;
+    if (j.idx == nullptr || j.rotation == nullptr || j.codebook == nullptr || j.out == nullptr) return TQ_ENULL;
+  }
+  for (int i = 0; i < n_jobs; ++i) {
+    int rc = tq::simt_dequantize(jobs[i], (cudaStream_t)stream);
+    if (rc != TQ_OK) return rc;
+  }
+  return TQ_OK;
+}
+
+int tq_project(const void* x, int x_dtype, int64_t n, int K, const float* m, int N, float* out, void* stream) {
+  if (K < 1 || K > TQ_MAX_DIM || N < 1 || N > TQ_MAX_DIM) return TQ_EDIM;
+  if (bad_dtype(x_dtype)) return TQ_EDTYPE;
+  if (n < 0) return TQ_EINVAL;
+  if (n == 0) return TQ_OK;
+  if (x == nullptr || m == nullptr || out == nullptr) return TQ_ENULL;
+  return tq::simt_project(x, x_dtype, n, K, m, N, out, (cudaStream_t)stream);
+}
+
+size_t tq_score_workspace_bytes(int64_t B, int64_t Hq, int64_t Sq, int64_t Sk, int D) {
+  if (B < 0 || Hq < 0 || Sq < 0 || Sk < 0 || D < 1) return 0;
+  return tq::simt_score_workspace(B, Hq, Sq, Sk, D);
+}
+
+int tq_score_packed(const TqScoreJob* job, void* stream) {
+  if (job == nullptr) return TQ_ENULL;
+  int rc = check_common(job->D, job->bits);
+  if (rc != TQ_OK) return rc;
+  if (bad_dtype(job->q_dtype)) return TQ_EDTYPE;
+  if (job->B < 0 || job->Hq < 0 || job->Sq < 0 || job->Hkv < 1 || job->Sk < 0 || job->Hq % job->Hkv != 0) return TQ_EINVAL;
+  if (job->B * job->Hq * job->Sq == 0 || job->Sk == 0) return TQ_OK;
+  if (job->q == nullptr || job->idx_bytes == nullptr || job->norms == nullptr || job->rotation_t == nullptr ||
+      job->codebook == nullptr || job->logits == nullptr || job->workspace == nullptr)
+    return TQ_ENULL;
+  if (((uintptr_t)job->workspace & 255u) != 0) return TQ_EALIGN;
+  if (job->workspace_bytes < tq::simt_score_workspace(job->B, job->Hq, job->Sq, job->Sk, job->D)) return TQ_EWORKSPACE;
+  return tq::simt_score_packed(*job, (cudaStream_t)stream);
+}
+
+int tq_qjl_compress(const TqQjlCompressJob* job, void* stream) {
+  if (job == nullptr) return TQ_ENULL;
+  int rc = check_common(job->D, job->bits);
+  if (rc != TQ_OK) return rc;
+  if (job->M < 1 || job->M > TQ_MAX_DIM) return TQ_EDIM;
+  if (bad_dtype(job->x_dtype)) return TQ_EDTYPE;
+  if (job->rnorm_dtype != TQ_F16 && job->rnorm_dtype != TQ_F32) return TQ_EDTYPE;
+  if (job->B < 0 || job->H < 0 || job->S < 0 || (job->signs_dtype != 0 && job->signs_dtype != 1)) return TQ_EINVAL;
+  if (job->idx_out != nullptr && job->idx_mode != TQ_IDX_U8 && job->idx_mode != TQ_IDX_I64) return TQ_EINVAL;
+  if (job->B * job->H * job->S == 0) return TQ_OK;
+  if (job->x == nullptr || job->rotation_t == nullptr || job->rotation == nullptr || job->codebook == nullptr ||
+      job->qjl_t == nullptr || job->signs_out == nullptr || job->rnorm_out == nullptr)
+    return TQ_ENULL;
+  return tq::simt_qjl_compress(*job, (cudaStream_t)stream);
+}
+
+size_t tq_qjl_scores_workspace_bytes(int64_t BH, int64_t Sq, int D) {
+  if (BH < 0 || Sq < 0 || D < 1) return 0;
+  return tq::simt_qjl_scores_workspace(BH, Sq, D);
+}
+
+int tq_qjl_scores(const TqQjlScoreJob* job, void* stream) {
+  if (job == nullptr) return TQ_ENULL;
+  if (job->D < 1 || job->D > TQ_MAX_DIM) return TQ_EDIM;
+  if (bad_dtype(job->q_dtype)) return TQ_EDTYPE;
+  if (job->BH < 0 || job->Sq < 0 || job->Sk < 0) return TQ_EINVAL;
+  if (job->BH == 0 || job->Sq == 0 || job->Sk == 0) return TQ_OK;
+  if (job->q == nullptr || job->k_mse == nullptr || job->signs == nullptr || job->rnorm == nullptr ||
+      job->qjl_t == nullptr || job->scores == nullptr || job->workspace == nullptr)
+    return TQ_ENULL;
+  if (((uintptr_t)job->workspace & 15u) != 0) return TQ_EALIGN;
+  if (job->workspace_bytes < tq::simt_qjl_scores_workspace(job->BH, job->Sq, job->D)) return TQ_EWORKSPACE;
+  return tq::simt_qjl_scores(*job, (cudaStream_t)stream);
+}
+
+int tq_prod_inner_product(const float* y, int64_t ny, const int64_t* idx, const float* signs, const float* rnorm,
+                          int64_t n, int D, int M, const float* rotation, const float* codebook, const float* qjl_t,
+                          float* out, void* workspace, size_t workspace_bytes, void* stream) {
+  if (D < 1 || D > TQ_MAX_DIM || M < 1 || M > TQ_MAX_DIM) return TQ_EDIM;
+  if (n < 0 || (ny != n && ny != 1)) return TQ_EINVAL;
+  if (n == 0) return TQ_OK;
+  if (y == nullptr || idx == nullptr || signs == nullptr || rnorm == nullptr || rotation == nullptr ||
+      codebook == nullptr || qjl_t == nullptr || out == nullptr || workspace == nullptr)
+    return TQ_ENULL;
+  if (((uintptr_t)workspace & 15u) != 0) return TQ_EALIGN;
+  if (workspace_bytes < (size_t)(n + ny) * 256 * sizeof(float)) return TQ_EWORKSPACE;
+  return tq::simt_prod_inner_product(y, ny, idx, signs, rnorm, n, D, M, rotation, codebook, qjl_t, out, workspace,
+                                     (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,30 @@
+// Internal launch interface between the C ABI layer and the kernel files.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "../../include/turboquant_b200.h"
+
+namespace tq {
+
+int last_cuda_error();
+void note_cuda_error(int e);
+long long launch_count();
+int check_launch();   // cudaGetLastError -> TQ_OK / TQ_ELAUNCH, counts successful launches
+
+// FP32 CUDA-core path (tq_simt.cu)
+int simt_quantize_rotated(const float* y, int64_t n, int D, int bits, const float* cb, int mode, void* out,
+                          cudaStream_t st);
+int simt_quantize(const TqQuantizeJob& job, cudaStream_t st);
+int simt_dequantize(const TqDequantizeJob& job, cudaStream_t st);
+int simt_project(const void* x, int x_dtype, int64_t n, int K, const float* m, int N, float* out, cudaStream_t st);
+size_t simt_score_workspace(int64_t B, int64_t Hq, int64_t Sq, int64_t Sk, int D);
+int simt_score_packed(const TqScoreJob& job, cudaStream_t st);
+int simt_qjl_compress(const TqQjlCompressJob& job, cudaStream_t st);
+size_t simt_qjl_scores_workspace(int64_t BH, int64_t Sq, int D);
+int simt_qjl_scores(const TqQjlScoreJob& job, cudaStream_t st);
+int simt_prod_inner_product(const float* y, int64_t ny, const int64_t* idx, const float* signs, const float* rnorm,
+                            int64_t n, int D, int M, const float* rotation, const float* codebook, const float* qjl_t,
+                            float* out, void* workspace, cudaStream_t st);
+
+}  // namespace tq

@@ -1,0 +1,159 @@
+"""ctypes binding of libturboquant_b200.so (the C ABI in include/turboquant_b200.h).
+
+There is no fallback: if the library is missing, importing the compressors
+fails with instructions to build it, and every compute entry point refuses
+tensors that are not on a CUDA device.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libturboquant_b200.so")
+
+F32, F16, BF16 = 0, 1, 2
+IDX_PACKED, IDX_U8, IDX_I64 = 0, 1, 2
+CODEBOOK_FLOATS = 512
+
+_DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+
+class BitsError(ValueError, ZeroDivisionError):
+    """bits outside 1..8 (the reference fails with ZeroDivisionError in 8 // bits)."""
+
+
+class QuantizeJob(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("x_dtype", C.c_int32), ("D", C.c_int32), ("bits", C.c_int32),
+                ("normalize", C.c_int32), ("B", C.c_int64), ("H", C.c_int64), ("S", C.c_int64),
+                ("stride_b", C.c_int64), ("stride_h", C.c_int64), ("stride_s", C.c_int64),
+                ("rotation_t", C.c_void_p), ("codebook", C.c_void_p), ("idx_mode", C.c_int32),
+                ("reserved", C.c_int32), ("idx_out", C.c_void_p), ("norms_out", C.c_void_p)]
+
+
+class DequantizeJob(C.Structure):
+    _fields_ = [("idx", C.c_void_p), ("norms", C.c_void_p), ("idx_mode", C.c_int32), ("D", C.c_int32),
+                ("bits", C.c_int32), ("out_dtype", C.c_int32), ("B", C.c_int64), ("H", C.c_int64), ("S", C.c_int64),
+                ("out", C.c_void_p), ("ostride_b", C.c_int64), ("ostride_h", C.c_int64), ("ostride_s", C.c_int64),
+                ("rotation", C.c_void_p), ("codebook", C.c_void_p)]
+
+
+class ScoreJob(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("q_dtype", C.c_int32), ("D", C.c_int32), ("bits", C.c_int32),
+                ("reserved", C.c_int32), ("B", C.c_int64), ("Hq", C.c_int64), ("Sq", C.c_int64), ("Hkv", C.c_int64),
+                ("Sk", C.c_int64), ("idx_bytes", C.c_void_p), ("norms", C.c_void_p), ("rotation_t", C.c_void_p),
+                ("codebook", C.c_void_p), ("scale", C.c_float), ("reserved2", C.c_int32), ("logits", C.c_void_p),
+                ("probs", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
+class QjlCompressJob(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("x_dtype", C.c_int32), ("D", C.c_int32), ("bits", C.c_int32),
+                ("normalize", C.c_int32), ("B", C.c_int64), ("H", C.c_int64), ("S", C.c_int64),
+                ("stride_b", C.c_int64), ("stride_h", C.c_int64), ("stride_s", C.c_int64),
+                ("rotation_t", C.c_void_p), ("rotation", C.c_void_p), ("codebook", C.c_void_p), ("qjl_t", C.c_void_p),
+                ("M", C.c_int32), ("signs_dtype", C.c_int32), ("rnorm_dtype", C.c_int32), ("idx_mode", C.c_int32),
+                ("k_mse_out", C.c_void_p), ("idx_out", C.c_void_p), ("signs_out", C.c_void_p), ("rnorm_out", C.c_void_p)]
+
+
+class QjlScoreJob(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("q_dtype", C.c_int32), ("D", C.c_int32), ("BH", C.c_int64), ("Sq", C.c_int64),
+                ("Sk", C.c_int64), ("k_mse", C.c_void_p), ("signs", C.c_void_p), ("rnorm", C.c_void_p),
+                ("qjl_t", C.c_void_p), ("scores", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
+_lib = None
+
+
+def lib():
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python turboquant-pytorch_b200/build.py` "
+            "(nvcc, sm_100a).  There is no CPU or PyTorch fallback for the compression kernels.")
+    L = C.CDLL(LIB_PATH)
+    vp, i32, i64, sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
+    L.tq_version.restype = i32
+    L.tq_strerror.restype = C.c_char_p
+    L.tq_strerror.argtypes = [i32]
+    L.tq_last_cuda_error.restype = i32
+    L.tq_launch_count.restype = i64
+    L.tq_packed_row_bytes.argtypes = [i32, i32]
+    L.tq_build_codebook.argtypes = [vp, i32, vp]
+    L.tq_quantize_rotated.argtypes = [vp, i64, i32, i32, vp, i32, vp, vp]
+    L.tq_quantize.argtypes = [C.POINTER(QuantizeJob), i32, vp]
+    L.tq_dequantize.argtypes = [C.POINTER(DequantizeJob), i32, vp]
+    L.tq_project.argtypes = [vp, i32, i64, i32, vp, i32, vp, vp]
+    L.tq_score_workspace_bytes.restype = sz
+    L.tq_score_workspace_bytes.argtypes = [i64, i64, i64, i64, i32]
+    L.tq_score_packed.argtypes = [C.POINTER(ScoreJob), vp]
+    L.tq_qjl_compress.argtypes = [C.POINTER(QjlCompressJob), vp]
+    L.tq_qjl_scores_workspace_bytes.restype = sz
+    L.tq_qjl_scores_workspace_bytes.argtypes = [i64, i64, i32]
+    L.tq_qjl_scores.argtypes = [C.POINTER(QjlScoreJob), vp]
+    L.tq_prod_inner_product.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, vp, vp, vp, vp, sz, vp]
+    for name in ("tq_packed_row_bytes", "tq_build_codebook", "tq_quantize_rotated", "tq_quantize", "tq_dequantize",
+                 "tq_project", "tq_score_packed", "tq_qjl_compress", "tq_qjl_scores", "tq_prod_inner_product"):
+        getattr(L, name).restype = i32
+    _lib = L
+    return L
+
+
+def check(rc: int, what: str):
+    """Map a TQ_E* code to the Python exception a caller of the reference would expect."""
+    if rc == 0:
+        return
+    msg = f"{what}: {lib().tq_strerror(rc).decode()} (code {rc})"
+    if rc == -2:
+        raise BitsError(msg)
+    if rc in (-1, -3, -4, -5, -6, -8, -9):
+        raise ValueError(msg)
+    if rc == -7:
+        msg += f"; cudaError {lib().tq_last_cuda_error()}"
+    raise RuntimeError(msg)
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise ValueError(f"unsupported dtype {t.dtype}; use float32, float16 or bfloat16") from None
+
+
+def require_cuda(t: torch.Tensor, what: str):
+    if not t.is_cuda:
+        raise RuntimeError(f"{what}: tensor is on {t.device}; the compression kernels run on CUDA (sm_100a) only "
+                           "and there is no CPU path")
+
+
+def stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def packed_row_bytes(D: int, bits: int) -> int:
+    if not 1 <= bits <= 8:
+        raise BitsError(f"bits must be in 1..8, got {bits}")
+    ipb = 8 // bits
+    return (D + ipb - 1) // ipb
+
+
+def codebook_block(centroids: torch.Tensor, bits: int) -> torch.Tensor:
+    """512-float device-format block (centroids + exact decision thresholds), on the CPU."""
+    c = centroids.detach().to("cpu", torch.float32).contiguous()
+    if c.numel() != 2 ** bits:
+        raise ValueError(f"expected {2 ** bits} centroids, got {c.numel()}")
+    block = torch.empty(CODEBOOK_FLOATS, dtype=torch.float32)
+    check(lib().tq_build_codebook(c.data_ptr(), bits, block.data_ptr()), "tq_build_codebook")
+    return block
+
+
+def bhs_strides(t: torch.Tensor):
+    """(tensor with unit last stride, stride_b, stride_h, stride_s) of a (B,H,S,D) tensor."""
+    if t.stride(-1) != 1 and t.shape[-1] > 1:
+        t = t.contiguous()
+    return t, t.stride(0), t.stride(1), t.stride(2)

@@ -1,0 +1,186 @@
+"""Tensor-level wrappers over the C ABI: allocate outputs with torch, pass raw pointers.
+
+Every function here runs on the tensors' CUDA device and on torch's current
+stream; nothing synchronises.  Outputs are freshly allocated torch tensors.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _native as N
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def quantize_job(x: torch.Tensor, pi_t: torch.Tensor, codebook: torch.Tensor, bits: int, normalize: bool,
+                 idx_mode: int):
+    """Prepare one quantise job for a (B,H,S,D) tensor; returns (job, idx_out, norms_out, keepalive)."""
+    N.require_cuda(x, "quantize")
+    B, H, S, D = x.shape
+    x, sb, sh, ss = N.bhs_strides(x)
+    n = B * H * S
+    if idx_mode == N.IDX_PACKED:
+        idx = torch.empty((B, H, S, N.packed_row_bytes(D, bits)), dtype=torch.uint8, device=x.device)
+    elif idx_mode == N.IDX_U8:
+        idx = torch.empty((n, D), dtype=torch.uint8, device=x.device)
+    else:
+        idx = torch.empty((n, D), dtype=torch.int64, device=x.device)
+    norms = torch.empty((B, H, S), dtype=torch.float16, device=x.device) if normalize else None
+    job = N.QuantizeJob(x=x.data_ptr(), x_dtype=N.dtype_code(x), D=D, bits=bits, normalize=int(normalize),
+                        B=B, H=H, S=S, stride_b=sb, stride_h=sh, stride_s=ss, rotation_t=pi_t.data_ptr(),
+                        codebook=codebook.data_ptr(), idx_mode=idx_mode, reserved=0, idx_out=idx.data_ptr(),
+                        norms_out=_ptr(norms))
+    return job, idx, norms, x
+
+
+def run_quantize(jobs: Sequence[N.QuantizeJob], device):
+    arr = (N.QuantizeJob * len(jobs))(*jobs)
+    with torch.cuda.device(device):
+        N.check(N.lib().tq_quantize(arr, len(jobs), N.stream_ptr(device)), "tq_quantize")
+
+
+def dequantize_job(idx: torch.Tensor, norms: Optional[torch.Tensor], shape, pi: torch.Tensor, codebook: torch.Tensor,
+                   bits: int, idx_mode: int, out: torch.Tensor):
+    """One dequantise job writing into `out`, a (B,H,S,D) tensor or strided view with unit last stride."""
+    N.require_cuda(idx, "dequantize")
+    B, H, S, D = shape
+    if not idx.is_contiguous():
+        idx = idx.contiguous()
+    if norms is not None and not norms.is_contiguous():
+        norms = norms.contiguous()
+    assert out.stride(-1) == 1 or D == 1
+    job = N.DequantizeJob(idx=idx.data_ptr(), norms=_ptr(norms), idx_mode=idx_mode, D=D, bits=bits,
+                          out_dtype=N.dtype_code(out), B=B, H=H, S=S, out=out.data_ptr(), ostride_b=out.stride(0),
+                          ostride_h=out.stride(1), ostride_s=out.stride(2), rotation=pi.data_ptr(),
+                          codebook=codebook.data_ptr())
+    return job, (idx, norms)
+
+
+def run_dequantize(jobs: Sequence[N.DequantizeJob], device):
+    arr = (N.DequantizeJob * len(jobs))(*jobs)
+    with torch.cuda.device(device):
+        N.check(N.lib().tq_dequantize(arr, len(jobs), N.stream_ptr(device)), "tq_dequantize")
+
+
+def project(x: torch.Tensor, m: torch.Tensor) -> torch.Tensor:
+    """x (..., K) @ m (K, N) -> fp32 (..., N)."""
+    N.require_cuda(x, "project")
+    K, n_out = m.shape
+    flat = x.reshape(-1, K)
+    if not flat.is_contiguous():
+        flat = flat.contiguous()
+    out = torch.empty((flat.shape[0], n_out), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        N.check(N.lib().tq_project(flat.data_ptr(), N.dtype_code(flat), flat.shape[0], K, m.data_ptr(), n_out,
+                                   out.data_ptr(), N.stream_ptr(x.device)), "tq_project")
+    return out.reshape(*x.shape[:-1], n_out)
+
+
+def quantize_rotated(y: torch.Tensor, codebook: torch.Tensor, bits: int, idx_mode: int = N.IDX_PACKED) -> torch.Tensor:
+    """Rotated fp32 values (n, D) -> indices in the given layout."""
+    N.require_cuda(y, "quantize_rotated")
+    y = y.contiguous().float()
+    n, D = y.shape
+    if idx_mode == N.IDX_PACKED:
+        out = torch.empty((n, N.packed_row_bytes(D, bits)), dtype=torch.uint8, device=y.device)
+    elif idx_mode == N.IDX_U8:
+        out = torch.empty((n, D), dtype=torch.uint8, device=y.device)
+    else:
+        out = torch.empty((n, D), dtype=torch.int64, device=y.device)
+    with torch.cuda.device(y.device):
+        N.check(N.lib().tq_quantize_rotated(y.data_ptr(), n, D, bits, codebook.data_ptr(), idx_mode, out.data_ptr(),
+                                            N.stream_ptr(y.device)), "tq_quantize_rotated")
+    return out
+
+
+def score_packed(q: torch.Tensor, idx_bytes: torch.Tensor, norms: torch.Tensor, pi_t: torch.Tensor,
+                 codebook: torch.Tensor, bits: int, scale: float = 1.0, softmax: bool = False):
+    """q (B,Hq,Sq,D); packed keys (B,Hkv,Sk,G) + norms (B,Hkv,Sk) -> logits (B,Hq,Sq,Sk) [, probs]."""
+    N.require_cuda(q, "score_packed")
+    B, Hq, Sq, D = q.shape
+    _, Hkv, Sk, _G = idx_bytes.shape
+    q = q.contiguous()
+    idx_bytes = idx_bytes.contiguous()
+    norms = norms.contiguous()
+    logits = torch.empty((B, Hq, Sq, Sk), dtype=torch.float32, device=q.device)
+    probs = torch.empty_like(logits) if softmax else None
+    L = N.lib()
+    ws_bytes = L.tq_score_workspace_bytes(B, Hq, Sq, Sk, D)
+    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=q.device)
+    job = N.ScoreJob(q=q.data_ptr(), q_dtype=N.dtype_code(q), D=D, bits=bits, reserved=0, B=B, Hq=Hq, Sq=Sq, Hkv=Hkv,
+                     Sk=Sk, idx_bytes=idx_bytes.data_ptr(), norms=norms.data_ptr(), rotation_t=pi_t.data_ptr(),
+                     codebook=codebook.data_ptr(), scale=float(scale), reserved2=0, logits=logits.data_ptr(),
+                     probs=_ptr(probs), workspace=ws.data_ptr(), workspace_bytes=ws.numel())
+    with torch.cuda.device(q.device):
+        N.check(L.tq_score_packed(C.byref(job), N.stream_ptr(q.device)), "tq_score_packed")
+    return (logits, probs) if softmax else logits
+
+
+def qjl_compress(x: torch.Tensor, pi: torch.Tensor, pi_t: torch.Tensor, codebook: torch.Tensor, qjl_t: torch.Tensor,
+                 bits: int, normalize: bool, want_k_mse: bool, idx_mode: Optional[int], signs_fp32: bool,
+                 rnorm_fp32: bool):
+    """MSE stage + QJL signs for a (B,H,S,D) tensor.  Returns (k_mse|None, idx|None, signs (n,M), rnorm (n,))."""
+    N.require_cuda(x, "qjl_compress")
+    B, H, S, D = x.shape
+    x, sb, sh, ss = N.bhs_strides(x)
+    n = B * H * S
+    M = qjl_t.shape[1]
+    dev = x.device
+    k_mse = torch.empty((n, D), dtype=torch.float16, device=dev) if want_k_mse else None
+    idx = None
+    if idx_mode is not None:
+        idx = torch.empty((n, D), dtype=torch.int64 if idx_mode == N.IDX_I64 else torch.uint8, device=dev)
+    signs = torch.empty((n, M), dtype=torch.float32 if signs_fp32 else torch.int8, device=dev)
+    rnorm = torch.empty((n,), dtype=torch.float32 if rnorm_fp32 else torch.float16, device=dev)
+    job = N.QjlCompressJob(x=x.data_ptr(), x_dtype=N.dtype_code(x), D=D, bits=bits, normalize=int(normalize), B=B, H=H,
+                           S=S, stride_b=sb, stride_h=sh, stride_s=ss, rotation_t=pi_t.data_ptr(),
+                           rotation=pi.data_ptr(), codebook=codebook.data_ptr(), qjl_t=qjl_t.data_ptr(), M=M,
+                           signs_dtype=int(signs_fp32), rnorm_dtype=N.F32 if rnorm_fp32 else N.F16,
+                           idx_mode=idx_mode if idx_mode is not None else N.IDX_U8, k_mse_out=_ptr(k_mse),
+                           idx_out=_ptr(idx), signs_out=signs.data_ptr(), rnorm_out=rnorm.data_ptr())
+    with torch.cuda.device(dev):
+        N.check(N.lib().tq_qjl_compress(C.byref(job), N.stream_ptr(dev)), "tq_qjl_compress")
+    return k_mse, idx, signs, rnorm
+
+
+def qjl_scores(q: torch.Tensor, k_mse: torch.Tensor, signs: torch.Tensor, rnorm: torch.Tensor,
+               qjl_t: torch.Tensor) -> torch.Tensor:
+    """q (B,H,Sq,D) against the compressed dict tensors -> (B,H,Sq,Sk) fp32."""
+    N.require_cuda(q, "qjl_scores")
+    B, H, Sq, D = q.shape
+    Sk = k_mse.shape[2]
+    q = q.contiguous()
+    k_mse, signs, rnorm = k_mse.contiguous(), signs.contiguous(), rnorm.contiguous()
+    out = torch.empty((B, H, Sq, Sk), dtype=torch.float32, device=q.device)
+    L = N.lib()
+    ws_bytes = L.tq_qjl_scores_workspace_bytes(B * H, Sq, D)
+    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=q.device)
+    job = N.QjlScoreJob(q=q.data_ptr(), q_dtype=N.dtype_code(q), D=D, BH=B * H, Sq=Sq, Sk=Sk, k_mse=k_mse.data_ptr(),
+                        signs=signs.data_ptr(), rnorm=rnorm.data_ptr(), qjl_t=qjl_t.data_ptr(), scores=out.data_ptr(),
+                        workspace=ws.data_ptr(), workspace_bytes=ws.numel())
+    with torch.cuda.device(q.device):
+        N.check(L.tq_qjl_scores(C.byref(job), N.stream_ptr(q.device)), "tq_qjl_scores")
+    return out
+
+
+def prod_inner_product(y: torch.Tensor, idx: torch.Tensor, signs: torch.Tensor, rnorm: torch.Tensor, pi: torch.Tensor,
+                       codebook: torch.Tensor, qjl_t: torch.Tensor) -> torch.Tensor:
+    """Row-paired estimator; y is (n, D) or a single row (1, D)."""
+    N.require_cuda(idx, "prod_inner_product")
+    n, D = idx.shape
+    M = signs.shape[1]
+    y = y.float().contiguous()
+    out = torch.empty((n,), dtype=torch.float32, device=idx.device)
+    ws = torch.empty(max((n + y.shape[0]) * 256 * 4, 256), dtype=torch.uint8, device=idx.device)
+    with torch.cuda.device(idx.device):
+        N.check(N.lib().tq_prod_inner_product(
+            y.data_ptr(), y.shape[0], idx.contiguous().data_ptr(), signs.contiguous().data_ptr(),
+            rnorm.contiguous().data_ptr(), n, D, M, pi.data_ptr(), codebook.data_ptr(), qjl_t.data_ptr(),
+            out.data_ptr(), ws.data_ptr(), ws.numel(), N.stream_ptr(idx.device)), "tq_prod_inner_product")
+    return out
