@@ -32,7 +32,8 @@ def generate_rotation_matrix(d: int, seed: Optional[int] = None, device: str = "
     q, r = torch.linalg.qr(_seeded_gaussian(d, d, seed))
     flip = torch.sign(torch.diag(r))
     flip[flip == 0] = 1.0
-    return (q * flip.unsqueeze(0)).to(device)
+    # LAPACK hands Q back column-major; the kernels take raw pointers, so fix the layout here
+    return (q * flip.unsqueeze(0)).contiguous().to(device)
 
 
 def generate_qjl_matrix(d: int, m: Optional[int] = None, seed: Optional[int] = None, device: str = "cpu") -> torch.Tensor:
