@@ -166,6 +166,24 @@ size_t tq_score_workspace_bytes(int64_t B, int64_t Hq, int64_t Sq, int64_t Sk, i
  * Replaces: compress -> decompress -> matmul of turboquant/validate_v3.py:83-87.  */
 int tq_score_packed(const TqScoreJob* job, void* stream);
 
+/* Same computation and results as tq_score_packed, for callers that cannot
+ * provide scratch memory: hosts whose device memory is fully planned by another
+ * framework, request paths that must stay off the allocator, or bindings that
+ * can only pass the tensors they own.  job->workspace and workspace_bytes are
+ * ignored; the scratch is a fixed array of TQ_SCORE_NOALLOC_SCRATCH_BYTES inside
+ * the library image (each GPU that loads the library holds it until exit).  The
+ * call allocates and frees nothing.  It returns TQ_ETOOBIG when
+ * tq_score_workspace_bytes(B, Hq, Sq, Sk, D) exceeds that size.  The first call
+ * on a device looks up the array's address (cudaGetSymbolAddress) with that
+ * device current, so make the first call on each device before any stream
+ * capture.  All calls on a device share the array, which keeps the previous
+ * call's contents (nothing in it needs clearing); two calls whose kernels can
+ * overlap on the GPU -- different streams without an ordering between them --
+ * race on it, so keep such calls on one stream or order them with events.
+ * This entry point has no counterpart in the reference.                       */
+#define TQ_SCORE_NOALLOC_SCRATCH_BYTES (4u << 20)
+int tq_score_packed_noalloc(const TqScoreJob* job, void* stream);
+
 /* ---- K4: MSE stage + QJL sign stage ------------------------------------ */
 typedef struct {
   const void* x; int32_t x_dtype; int32_t D;

@@ -18,6 +18,7 @@ LIB_PATH = os.path.join(_HERE, "libturboquant_b200.so")
 F32, F16, BF16 = 0, 1, 2
 IDX_PACKED, IDX_U8, IDX_I64 = 0, 1, 2
 CODEBOOK_FLOATS = 512
+SCORE_NOALLOC_SCRATCH_BYTES = 4 << 20
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
@@ -92,13 +93,14 @@ def lib():
     L.tq_score_workspace_bytes.restype = sz
     L.tq_score_workspace_bytes.argtypes = [i64, i64, i64, i64, i32]
     L.tq_score_packed.argtypes = [C.POINTER(ScoreJob), vp]
+    L.tq_score_packed_noalloc.argtypes = [C.POINTER(ScoreJob), vp]
     L.tq_qjl_compress.argtypes = [C.POINTER(QjlCompressJob), vp]
     L.tq_qjl_scores_workspace_bytes.restype = sz
     L.tq_qjl_scores_workspace_bytes.argtypes = [i64, i64, i32]
     L.tq_qjl_scores.argtypes = [C.POINTER(QjlScoreJob), vp]
     L.tq_prod_inner_product.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, vp, vp, vp, vp, sz, vp]
     for name in ("tq_packed_row_bytes", "tq_build_codebook", "tq_quantize_rotated", "tq_quantize", "tq_dequantize",
-                 "tq_project", "tq_score_packed", "tq_qjl_compress", "tq_qjl_scores", "tq_prod_inner_product"):
+                 "tq_project", "tq_score_packed", "tq_score_packed_noalloc", "tq_qjl_compress", "tq_qjl_scores", "tq_prod_inner_product"):
         getattr(L, name).restype = i32
     _lib = L
     return L

@@ -122,6 +122,31 @@ def score_packed(q: torch.Tensor, idx_bytes: torch.Tensor, norms: torch.Tensor, 
     return (logits, probs) if softmax else logits
 
 
+def score_packed_noalloc(q: torch.Tensor, idx_bytes: torch.Tensor, norms: torch.Tensor, pi_t: torch.Tensor,
+                          codebook: torch.Tensor, bits: int, logits: torch.Tensor, probs: Optional[torch.Tensor] = None,
+                          scale: float = 1.0):
+    """score_packed for callers that bring every buffer themselves and may not allocate.
+
+    `logits` (and `probs`, if wanted) are caller-owned (B,Hq,Sq,Sk) fp32 tensors; the
+    scratch comes from the library's built-in 4 MiB array, so this wrapper creates no
+    tensor.  Inputs must already be contiguous.  Raises ValueError when the problem
+    needs more scratch than the built-in array holds.
+    """
+    N.require_cuda(q, "score_packed_noalloc")
+    B, Hq, Sq, D = q.shape
+    _, Hkv, Sk, _G = idx_bytes.shape
+    for t in (q, idx_bytes, norms, logits) + ((probs,) if probs is not None else ()):
+        if not t.is_contiguous():
+            raise ValueError("score_packed_noalloc takes contiguous tensors (it will not make copies)")
+    job = N.ScoreJob(q=q.data_ptr(), q_dtype=N.dtype_code(q), D=D, bits=bits, reserved=0, B=B, Hq=Hq, Sq=Sq, Hkv=Hkv,
+                     Sk=Sk, idx_bytes=idx_bytes.data_ptr(), norms=norms.data_ptr(), rotation_t=pi_t.data_ptr(),
+                     codebook=codebook.data_ptr(), scale=float(scale), reserved2=0, logits=logits.data_ptr(),
+                     probs=_ptr(probs), workspace=None, workspace_bytes=0)
+    with torch.cuda.device(q.device):
+        N.check(N.lib().tq_score_packed_noalloc(C.byref(job), N.stream_ptr(q.device)), "tq_score_packed_noalloc")
+    return logits if probs is None else (logits, probs)
+
+
 def qjl_compress(x: torch.Tensor, pi: torch.Tensor, pi_t: torch.Tensor, codebook: torch.Tensor, qjl_t: torch.Tensor,
                  bits: int, normalize: bool, want_k_mse: bool, idx_mode: Optional[int], signs_fp32: bool,
                  rnorm_fp32: bool):
