@@ -80,6 +80,18 @@ int tq_packed_row_bytes(int D, int bits);
  * [host].  Replaces the argmin rule of turboquant/compressors_v3.py:60-61.    */
 int tq_build_codebook(const float* centroids, int bits, float* block512);
 
+/* Tensor-core operand image of a (D, D) row-major fp32 matrix m [dev]: two fp16 pieces
+ * (m = hi + lo), K-major, 128-byte swizzled, tq_rotation_image_bytes(D) bytes (0 when D
+ * has no tensor-core path; only D = 128 has one).  Built once per compressor.
+ * For TqQuantizeJob pass m = Pi; for TqDequantizeJob pass m = Pi^T.
+ * Replaces nothing in the reference (a constant of this implementation).       */
+size_t tq_rotation_image_bytes(int D);
+int tq_prepare_rotation_image(const float* m, int D, void* image, void* stream);
+
+/* Status word written by a kernel whose bounded wait ran out: 0 = none, else
+ * (role << 16) | block.  Reads the device synchronously; for diagnostics only. */
+int tq_last_device_status(void);
+
 /* ---- K0: rotated fp32 values -> indices (the bit-exact gate) ----------- */
 /* y [dev] (n, D) contiguous fp32; out [dev] laid out per idx_mode.
  * Replaces: turboquant/compressors_v3.py:60-74, turboquant/lloyd_max.py:117-121. */
@@ -101,6 +113,9 @@ typedef struct {
   int32_t reserved;
   void* idx_out;          /* [dev] (B*H*S, row) contiguous                                   */
   uint16_t* norms_out;    /* [dev] fp16 bit patterns (B*H*S); may be NULL when normalize==0  */
+  const void* rotation_image; /* [dev] optional: tq_prepare_rotation_image(Pi) output.  With it, head_dim
+                             128, 16-bit x, normalize=1 and TQ_IDX_PACKED the job runs on the tensor
+                             cores; NULL keeps it on the FP32 path                              */
 } TqQuantizeJob;
 
 /* Runs n_jobs independent jobs [host array].

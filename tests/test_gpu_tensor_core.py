@@ -1,0 +1,124 @@
+"""The tcgen05 quantise kernel against the FP32 kernel and the oracle.
+
+Jobs with head_dim 128, 16-bit input and packed output run on the tensor cores;
+setting TQ_FORCE_SIMT=1 sends the same call down the FP32 path, which gives an
+in-library second opinion on top of the CPU oracle.
+"""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import tq_oracle as O
+from conftest import bits16
+
+import turboquant as tq
+from turboquant import _native as N
+from turboquant import batched
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _simt(fn):
+    os.environ["TQ_FORCE_SIMT"] = "1"
+    try:
+        return fn()
+    finally:
+        os.environ.pop("TQ_FORCE_SIMT", None)
+
+
+def _compare(c_tc, c_ref, bits, d=128, min_agree=0.9999):
+    a = O.unpack_indices(c_tc["idx_bytes"].cpu().numpy().reshape(-1, c_tc["idx_bytes"].shape[-1]), bits, d)
+    b = O.unpack_indices(c_ref["idx_bytes"].cpu().numpy().reshape(-1, c_ref["idx_bytes"].shape[-1]), bits, d)
+    agree = float((a == b).mean())
+    assert agree >= min_agree, agree
+    assert np.abs(a.astype(np.int64) - b).max() <= 1
+    g = bits16(c_tc["vec_norms"]).astype(np.int32)
+    w = bits16(c_ref["vec_norms"]).astype(np.int32)
+    assert np.abs(g - w).max() <= 1
+
+
+def _oracle_check(c, x_cpu, comp, bits, min_agree=0.9999):
+    cent, bnd = O.lloyd_max(128, bits)
+    _flat, norms, rot = O.rotate_unit(x_cpu, comp.Pi.cpu())
+    want = O.nearest_centroid(rot, cent).numpy()
+    got = O.unpack_indices(c["idx_bytes"].cpu().numpy().reshape(want.shape[0], -1), bits, 128)
+    bad = np.argwhere(got != want)
+    for r, col in bad[:2000]:
+        assert abs(int(got[r, col]) - int(want[r, col])) == 1
+        assert np.min(np.abs(bnd.numpy() - rot[r, col].item())) < 1e-6
+    assert 1.0 - len(bad) / want.size >= min_agree
+    g = bits16(c["vec_norms"]).astype(np.int32).reshape(-1)
+    w = bits16(norms.to(torch.float16)).astype(np.int32).reshape(-1)
+    assert np.abs(g - w).max() <= 1
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bits", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_tensor_core_quantize_matches_fp32_path_and_oracle(dtype, bits):
+    x = O.synthetic_kv((2, 3, 333, 128), dtype, seed=900 + bits)         # ragged: 333 = 2 tiles + 77 rows per slab
+    comp = tq.MSECompressor(128, bits, seed=70 + bits, device=DEV)
+    assert comp._img_q is not None
+    xg = x.to(DEV)
+    c_tc = comp.compress(xg)
+    c_ref = _simt(lambda: comp.compress(xg))
+    torch.cuda.synchronize()
+    assert N.lib().tq_last_device_status() == 0
+    _compare(c_tc, c_ref, bits)
+    _oracle_check(c_tc, x, comp, bits)
+
+
+def test_tensor_core_path_reads_strided_views():
+    base = O.synthetic_kv((2, 4, 300, 128), torch.float16, seed=31)
+    g = base.to(DEV)
+    comp = tq.MSECompressor(128, 4, seed=3, device=DEV)
+    views = [(g[:, :, :172, :], base[:, :, :172, :]), (g[:, 1:3, 40:, :], base[:, 1:3, 40:, :]),
+             (g[1:, :, :, :], base[1:, :, :, :]),
+             (g.transpose(1, 2).contiguous().transpose(1, 2), base)]
+    for gv, cv in views:
+        c = comp.compress(gv)
+        _oracle_check(c, cv.contiguous(), comp, 4)
+        assert c["shape"] == tuple(cv.shape)
+    assert N.lib().tq_last_device_status() == 0
+
+
+def test_tensor_core_tiny_and_single_row_inputs():
+    comp = tq.MSECompressor(128, 4, seed=11, device=DEV)
+    for shape in ((1, 1, 1, 128), (1, 1, 127, 128), (1, 1, 128, 128), (1, 1, 129, 128), (3, 1, 5, 128), (1, 5, 2, 128)):
+        x = O.synthetic_kv(shape, torch.float16, seed=sum(shape))
+        c = comp.compress(x.to(DEV))
+        _oracle_check(c, x, comp, 4, min_agree=0.999)
+
+
+def test_many_layers_in_one_launch_match_per_layer_fp32_results():
+    L = 12
+    codecs = [tq.TurboQuantV3(128, key_bits=4, value_bits=2, residual_window=0, layer_idx=l, n_layers=L, protected_layers=2,
+                              device=DEV) for l in range(L)]
+    keys = [O.synthetic_kv((1, 2, 1000 + 64 * l, 128), torch.float16, 300 + l).to(DEV) for l in range(L)]
+    vals = [O.synthetic_kv((1, 2, 1000 + 64 * l, 128), torch.float16, 400 + l).to(DEV) for l in range(L)]
+    many = batched.compress_kv_layers(codecs, keys, vals)
+    ref = _simt(lambda: batched.compress_kv_layers(codecs, keys, vals))
+    torch.cuda.synchronize()
+    assert N.lib().tq_last_device_status() == 0
+    for l in range(L):
+        _compare(many[l][0]["compressed"], ref[l][0]["compressed"], codecs[l].key_bits)
+        _compare(many[l][1]["compressed"], ref[l][1]["compressed"], codecs[l].value_bits)
+
+
+def test_nan_and_zero_rows_on_the_tensor_core_path():
+    x = O.synthetic_kv((1, 1, 256, 128), torch.float16, seed=77)
+    x[0, 0, 3] = 0
+    x[0, 0, 9, 5] = float("nan")
+    x[0, 0, 200, 17] = float("inf")
+    comp = tq.MSECompressor(128, 4, seed=42, device=DEV)
+    c = comp.compress(x.to(DEV))
+    idx = c["idx_bytes"].cpu().numpy()[0, 0]
+    assert np.all(idx[3] == 0x77)
+    assert np.all(idx[9] == 0) and np.all(idx[200] == 0)
+    n = c["vec_norms"].cpu()[0, 0]
+    # an Inf coordinate meets both signs of the split rotation, so its norm comes out NaN here
+    # (the FP32 path and the reference give Inf); the indices are 0 either way
+    assert n[3].item() == 0 and torch.isnan(n[9]) and (torch.isinf(n[200]) or torch.isnan(n[200]))

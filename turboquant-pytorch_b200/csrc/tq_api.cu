@@ -92,6 +92,17 @@ int tq_build_codebook(const float* centroids, int bits, float* block) {
   return TQ_OK;
 }
 
+size_t tq_rotation_image_bytes(int D) { return tq::umma_rotation_image_bytes(D); }
+
+int tq_prepare_rotation_image(const float* m, int D, void* image, void* stream) {
+  if (m == nullptr || image == nullptr) return TQ_ENULL;
+  if (tq::umma_rotation_image_bytes(D) == 0) return TQ_EDIM;
+  if (((uintptr_t)image & 1023u) != 0) return TQ_EALIGN;
+  return tq::umma_prepare_rotation_image(m, D, image, (cudaStream_t)stream);
+}
+
+int tq_last_device_status(void) { return tq::umma_device_status(); }
+
 int tq_quantize_rotated(const float* y, int64_t n, int D, int bits, const float* codebook, int idx_mode, void* out,
                         void* stream) {
   int rc = check_common(D, bits);
@@ -116,8 +127,20 @@ int tq_quantize(const TqQuantizeJob* jobs, int n_jobs, void* stream) {
     if (j.x == nullptr || j.rotation_t == nullptr || j.codebook == nullptr || j.idx_out == nullptr) return TQ_ENULL;
     if (j.normalize && j.norms_out == nullptr) return TQ_ENULL;
   }
-  for (int i = 0; i < n_jobs; ++i) {
-    int rc = tq::simt_quantize(jobs[i], (cudaStream_t)stream);
+  // maximal runs of tensor-core-eligible jobs go out as one persistent launch each
+  int i = 0;
+  while (i < n_jobs) {
+    if (jobs[i].B * jobs[i].H * jobs[i].S == 0) { ++i; continue; }
+    int rc;
+    if (tq::umma_quantize_eligible(jobs[i])) {
+      int k = i + 1;
+      while (k < n_jobs && jobs[k].x_dtype == jobs[i].x_dtype && tq::umma_quantize_eligible(jobs[k])) ++k;
+      rc = tq::umma_quantize(jobs + i, k - i, (cudaStream_t)stream);
+      i = k;
+    } else {
+      rc = tq::simt_quantize(jobs[i], (cudaStream_t)stream);
+      ++i;
+    }
     if (rc != TQ_OK) return rc;
   }
   return TQ_OK;

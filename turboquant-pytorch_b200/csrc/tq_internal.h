@@ -27,4 +27,12 @@ int simt_prod_inner_product(const float* y, int64_t ny, const int64_t* idx, cons
                             int64_t n, int D, int M, const float* rotation, const float* codebook, const float* qjl_t,
                             float* out, void* workspace, cudaStream_t st);
 
+
+// tensor-core path (tq_umma.cu)
+size_t umma_rotation_image_bytes(int D);
+int umma_prepare_rotation_image(const float* m, int D, void* image, cudaStream_t st);
+bool umma_quantize_eligible(const TqQuantizeJob& job);
+int umma_quantize(const TqQuantizeJob* jobs, int n_jobs, cudaStream_t st);
+int umma_device_status();
+
 }  // namespace tq

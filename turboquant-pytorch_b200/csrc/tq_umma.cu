@@ -1,0 +1,575 @@
+// Tensor-core (tcgen05 / TMEM / TMA) kernels for the headline shape: head_dim 128,
+// 16-bit vectors, packed indices.
+//
+// quantize: a persistent, warp-specialised CTA per SM walks a contiguous range of
+// 128-vector tiles that may span several jobs (layers, K or V):
+//   warp 0      TMA producer: x tiles (two 128x64 boxes, 128-byte swizzle) into a
+//               4-stage shared-memory ring; the job's rotation image (64 KB) by bulk copy
+//   warp 1      issues tcgen05.mma kind::f16, M=128 N=128 K=16: 8 k-steps against the
+//               high fp16 piece of Pi and 8 against the low piece, all into ONE fp32
+//               accumulator of 128 TMEM columns (4 accumulators rotate)
+//   warps 2..17 epilogue, four warpgroups, one tile each: tcgen05.ld the accumulator
+//               (thread = vector, registers = coordinates), sum of squares -> norm
+//               (||Pi x|| = ||x||), scale, exact threshold search, bit pack, 16-byte stores
+// x is exact in fp16/bf16 and Pi = hi + lo to ~2^-22 (lo sits in fp16 subnormals, which
+// the tensor core handles), so the rotated values match an fp32 matmul to ~1e-8.
+// kind::f16 wants A and B in the same format (a bf16 A against an fp16 B is an illegal
+// instruction), so bf16 vectors run against three bf16 pieces of Pi (3 x 8 significant
+// bits) and a 3-stage ring; fp16 vectors use two fp16 pieces and a 4-stage ring.
+// Every mbarrier wait is bounded; on expiry the CTA raises an abort flag, records a
+// status word, drains its own copies and leaves through the normal exit.
+
+#include <cuda.h>
+
+#include <atomic>
+#include <cstdlib>
+
+#include "tq_common.cuh"
+#include "tq_internal.h"
+
+namespace tq {
+
+namespace {
+
+constexpr int kTileRows = 128;
+constexpr int kDim = 128;
+constexpr int kAccBufs = 4;
+constexpr int kEpiWarps = 16;
+constexpr int kThreads = 64 + kEpiWarps * 32;          // 576
+constexpr uint32_t kTileBytes = kTileRows * kDim * 2;  // 32768
+constexpr uint32_t kHalfBytes = kTileBytes / 2;        // one 64-column box
+constexpr uint32_t kImageBytes = 5 * kTileBytes;       // fp16 hi, lo; then bf16 p0, p1, p2
+constexpr int kMaxJobs = 96;
+constexpr uint32_t kSpinLimit = 1u << 22;              // bounded waits (each try_wait suspends for a while itself)
+
+// shared memory map (offsets from a 1024-byte aligned base)
+template <bool BF16>
+struct Cfg {
+  static constexpr int kStages = BF16 ? 3 : 4;
+  static constexpr int kPieces = BF16 ? 3 : 2;
+  static constexpr uint32_t kPieceOff = BF16 ? 2 * kTileBytes : 0;            // offset of the pieces in the image
+  static constexpr uint32_t kOffA = 0;
+  static constexpr uint32_t kOffPi = kOffA + kStages * kTileBytes;
+  static constexpr uint32_t kOffThr = kOffPi + kPieces * kTileBytes;          // 4 x 256 floats
+  static constexpr uint32_t kOffBar = kOffThr + 4 * 256 * 4;
+  static constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;                // + alignment slack
+};
+static_assert(Cfg<false>::kSmemBytes <= 232448 && Cfg<true>::kSmemBytes <= 232448, "shared memory budget");
+
+struct alignas(64) UmmaQuantJob {
+  CUtensorMap tmap;          // (D, S, H, B) view of x, box 64 x 128 x 1 x 1, 128-byte swizzle
+  const void* image;         // rotation image: hi piece then lo piece, swizzled K-major
+  const float* codebook;
+  uint8_t* idx_out;
+  uint16_t* norms_out;
+  int64_t S;
+  int32_t H;
+  int32_t tiles_per_slab;
+  int32_t tile_begin;        // first global tile of this job
+  int32_t bits;
+  int32_t a_bf16;
+  int32_t pad_;
+};
+
+struct UmmaQuantBatch {
+  int32_t n_jobs;
+  int32_t total_tiles;
+  int32_t* status;           // device status word (may be null)
+  UmmaQuantJob jobs[kMaxJobs];
+};
+
+static_assert(sizeof(UmmaQuantBatch) < 32000, "kernel parameter space");
+
+__device__ int g_umma_status;   // 0 = ok; otherwise (code << 16) | block
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait: false when the limit ran out or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 1023u) == 1023u && *abort_flag) return false;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t lo = (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16);
+  uint64_t hi = (uint64_t)(1024u >> 4) | ((uint64_t)1 << 14) | ((uint64_t)2 << 29);
+  return lo | (hi << 32);
+}
+
+__device__ __forceinline__ uint32_t idesc_f16(bool bf16) {
+  // D = fp32, A and B both fp16 or both bf16, K-major, N = 128, M = 128
+  const uint32_t fmt = bf16 ? 1u : 0u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+// job that owns `tile`; tiles only grow within a role, so the scan resumes from `from`
+__device__ __forceinline__ int find_job(const UmmaQuantBatch& b, int tile, int from) {
+  int j = from < 0 ? 0 : from;
+  while (j + 1 < b.n_jobs && tile >= b.jobs[j + 1].tile_begin) ++j;
+  return j;
+}
+
+// ---------------------------------------------------------------- epilogue
+// One thread owns one vector.  BITS is a compile-time constant so that the
+// search and the packing unroll completely.
+template <int BITS>
+__device__ __forceinline__ void epilogue_tile(uint32_t tmem_acc, const float* thr, uint8_t* idx_row, uint16_t* norm_ptr,
+                                              bool valid) {
+  constexpr int IPB = 8 / BITS;
+  constexpr int BYTES_PER_CHUNK = 32 / IPB;     // packed bytes per 32 coordinates
+  float ssq = 0.f;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    float v[32];
+    tmem_ld32(tmem_acc + c * 32, v);
+#pragma unroll
+    for (int e = 0; e < 32; ++e) ssq = fmaf(v[e], v[e], ssq);
+  }
+  const float norm = __fsqrt_rn(ssq);
+  const float inv = __fdiv_rn(1.0f, norm + 1e-8f);
+  if (valid) *norm_ptr = __half_as_ushort(__float2half_rn(norm));
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    float v[32];
+    tmem_ld32(tmem_acc + c * 32, v);
+    uint32_t words[BYTES_PER_CHUNK / 4 > 0 ? BYTES_PER_CHUNK / 4 : 1];
+#pragma unroll
+    for (int w = 0; w < BYTES_PER_CHUNK / 4; ++w) words[w] = 0u;
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      const float y = v[e] * inv;
+      int lo = 0, hi = (1 << BITS) - 1;
+#pragma unroll
+      for (int step = 0; step < BITS; ++step) {
+        const int mid = (lo + hi) >> 1;
+        if (y > thr[mid]) lo = mid + 1; else hi = mid;
+      }
+      // coordinate e of this chunk -> byte e / IPB, field (IPB-1 - e % IPB) of that byte
+      const int byte = e / IPB;
+      const int shift = 8 * (byte & 3) + BITS * (IPB - 1 - (e % IPB));
+      words[byte >> 2] |= (uint32_t)lo << shift;
+    }
+    if (valid) {
+      if constexpr (BYTES_PER_CHUNK == 4) {
+        *reinterpret_cast<uint32_t*>(idx_row + c * 4) = words[0];
+      } else if constexpr (BYTES_PER_CHUNK == 8) {
+        *reinterpret_cast<uint2*>(idx_row + c * 8) = make_uint2(words[0], words[1]);
+      } else if constexpr (BYTES_PER_CHUNK == 16) {
+        *reinterpret_cast<uint4*>(idx_row + c * 16) = make_uint4(words[0], words[1], words[2], words[3]);
+      } else {
+        *reinterpret_cast<uint4*>(idx_row + c * 32) = make_uint4(words[0], words[1], words[2], words[3]);
+        *reinterpret_cast<uint4*>(idx_row + c * 32 + 16) = make_uint4(words[4], words[5], words[6], words[7]);
+      }
+    }
+  }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_constant__ UmmaQuantBatch batch) {
+  constexpr int kStages = Cfg<BF16>::kStages;
+  constexpr int kPieces = Cfg<BF16>::kPieces;
+  constexpr uint32_t kOffA = Cfg<BF16>::kOffA, kOffPi = Cfg<BF16>::kOffPi, kOffThr = Cfg<BF16>::kOffThr,
+                     kOffBar = Cfg<BF16>::kOffBar;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t a_smem = base + kOffA;
+  const uint32_t pi_smem = base + kOffPi;
+  float* thr_all = reinterpret_cast<float*>(gbase + kOffThr);
+  const uint32_t bar0 = base + kOffBar;
+  // barrier slots (8 bytes each)
+  const uint32_t bar_full = bar0;                  // [kStages]
+  const uint32_t bar_empty = bar0 + 8 * kStages;   // [kStages]
+  const uint32_t bar_tfull = bar0 + 16 * kStages;  // [kAccBufs]
+  const uint32_t bar_tempty = bar_tfull + 8 * kAccBufs;
+  const uint32_t bar_pifull = bar_tempty + 8 * kAccBufs;
+  const uint32_t bar_pifree = bar_pifull + 8;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + kOffBar + 200);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + kOffBar + 208);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total = batch.total_tiles;
+  const int t0 = (int)((int64_t)total * blockIdx.x / gridDim.x);
+  const int t1 = (int)((int64_t)total * (blockIdx.x + 1) / gridDim.x);
+  const int n_local = t1 - t0;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) { mbar_init(bar_full + 8 * i, 1); mbar_init(bar_empty + 8 * i, 1); }
+    for (int i = 0; i < kAccBufs; ++i) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, 4); }
+    mbar_init(bar_pifull, 1);
+    mbar_init(bar_pifree, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int cur_job = -1, pi_loads = 0;
+      bool ok = true;
+      for (int i = 0; i < n_local && ok; ++i) {
+        const int t = t0 + i;
+        const int j = find_job(batch, t, cur_job);
+        const UmmaQuantJob& job = batch.jobs[j];
+        if (j != cur_job) {
+          if (pi_loads > 0) ok = mbar_wait(bar_pifree, (uint32_t)((pi_loads - 1) & 1), abort_flag);
+          if (!ok) break;
+          mbar_arrive_expect_tx(bar_pifull, kPieces * kTileBytes);
+          const uint8_t* img = reinterpret_cast<const uint8_t*>(job.image) + Cfg<BF16>::kPieceOff;
+#pragma unroll
+          for (int p = 0; p < kPieces; ++p) bulk_load(pi_smem + p * kTileBytes, img + p * kTileBytes, kTileBytes, bar_pifull);
+          ++pi_loads;
+          cur_job = j;
+        }
+        const int s = i % kStages;
+        ok = mbar_wait(bar_empty + 8 * s, (uint32_t)(((i / kStages) & 1) ^ 1), abort_flag);
+        if (!ok) break;
+        const int lt = t - job.tile_begin;
+        const int slab = lt / job.tiles_per_slab;
+        const int row0 = (lt - slab * job.tiles_per_slab) * kTileRows;
+        const int hh = slab % job.H, bb = slab / job.H;
+        mbar_arrive_expect_tx(bar_full + 8 * s, kTileBytes);
+        tma_load_4d(a_smem + s * kTileBytes, &job.tmap, 0, row0, hh, bb, bar_full + 8 * s);
+        tma_load_4d(a_smem + s * kTileBytes + kHalfBytes, &job.tmap, 64, row0, hh, bb, bar_full + 8 * s);
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        if (batch.status != nullptr) atomicCAS(batch.status, 0, (1 << 16) | (int)blockIdx.x);
+      }
+      // make sure none of this CTA's own copies is still in flight when it exits
+      const int armed = n_local < kStages ? n_local : kStages;
+      for (int k = 0; k < armed; ++k) {
+        const int i = n_local - 1 - k;
+        if (i >= 0) mbar_wait(bar_full + 8 * (i % kStages), (uint32_t)((i / kStages) & 1), abort_flag);
+      }
+      if (pi_loads > 0) mbar_wait(bar_pifull, (uint32_t)((pi_loads - 1) & 1), abort_flag);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int cur_job = -1, pi_uses = 0;
+      bool ok = true;
+      for (int i = 0; i < n_local && ok; ++i) {
+        const int t = t0 + i;
+        const int j = find_job(batch, t, cur_job);
+        if (j != cur_job) {
+          ok = mbar_wait(bar_pifull, (uint32_t)(pi_uses & 1), abort_flag);
+          if (!ok) break;
+          ++pi_uses;
+          cur_job = j;
+        }
+        const int s = i % kStages, b = i % kAccBufs;
+        ok = mbar_wait(bar_full + 8 * s, (uint32_t)((i / kStages) & 1), abort_flag);
+        if (!ok) break;
+        ok = mbar_wait(bar_tempty + 8 * b, (uint32_t)(((i / kAccBufs) & 1) ^ 1), abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t idesc = idesc_f16(BF16);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * 128);
+        const uint32_t a_tile = a_smem + s * kTileBytes;
+#pragma unroll
+        for (int piece = 0; piece < kPieces; ++piece) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t koff = (uint32_t)((k >> 2) * kHalfBytes + (k & 3) * 32);
+            const uint64_t adesc = smem_desc_sw128(a_tile + koff);
+            const uint64_t bdesc = smem_desc_sw128(pi_smem + piece * kTileBytes + koff);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (piece | k) != 0 ? 1u : 0u);
+          }
+        }
+        umma_commit(bar_empty + 8 * s);
+        umma_commit(bar_tfull + 8 * b);
+        const int next_job = (i + 1 < n_local) ? find_job(batch, t + 1, cur_job) : -1;
+        if (next_job != cur_job) umma_commit(bar_pifree);
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        if (batch.status != nullptr) atomicCAS(batch.status, 0, (2 << 16) | (int)blockIdx.x);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warpgroups
+    const int ew = warp - 2;
+    const int wg = ew >> 2;                    // 0..3, also the accumulator this group reads
+    const int quarter = warp & 3;              // TMEM lanes this warp may touch: 32*quarter ..
+    const int row = quarter * 32 + lane;
+    float* thr = thr_all + wg * 256;
+    const int wg_tid = (ew & 3) * 32 + lane;
+    int cur_job = -1;
+    bool ok = true;
+    for (int i = wg; i < n_local && ok; i += 4) {
+      const int t = t0 + i;
+      const int j = find_job(batch, t, cur_job);
+      const UmmaQuantJob& job = batch.jobs[j];
+      if (j != cur_job) {
+        asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");     // previous tile's readers are done
+        thr[wg_tid] = __ldg(job.codebook + kThresholdOff + wg_tid);
+        thr[wg_tid + 128] = __ldg(job.codebook + kThresholdOff + 128 + wg_tid);
+        asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");
+        cur_job = j;
+      }
+      ok = mbar_wait(bar_tfull + 8 * wg, (uint32_t)((i / kAccBufs) & 1), abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const int lt = t - job.tile_begin;
+      const int slab = lt / job.tiles_per_slab;
+      const int64_t s_row = (int64_t)(lt - slab * job.tiles_per_slab) * kTileRows + row;
+      const bool valid = s_row < job.S;
+      const int64_t n = (int64_t)slab * job.S + s_row;
+      const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(wg * 128);
+      const int ipb = 8 / job.bits;
+      uint8_t* idx_row = job.idx_out + n * (int64_t)(kDim / ipb);
+      uint16_t* norm_ptr = job.norms_out + n;
+      switch (job.bits) {
+        case 1: epilogue_tile<1>(tacc, thr, idx_row, norm_ptr, valid); break;
+        case 2: epilogue_tile<2>(tacc, thr, idx_row, norm_ptr, valid); break;
+        case 3: epilogue_tile<3>(tacc, thr, idx_row, norm_ptr, valid); break;
+        case 4: epilogue_tile<4>(tacc, thr, idx_row, norm_ptr, valid); break;
+        case 5: epilogue_tile<5>(tacc, thr, idx_row, norm_ptr, valid); break;
+        case 6: epilogue_tile<6>(tacc, thr, idx_row, norm_ptr, valid); break;
+        case 7: epilogue_tile<7>(tacc, thr, idx_row, norm_ptr, valid); break;
+        default: epilogue_tile<8>(tacc, thr, idx_row, norm_ptr, valid); break;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * wg);
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      if (batch.status != nullptr) atomicCAS(batch.status, 0, (3 << 16) | (int)blockIdx.x);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------- rotation image
+// image[piece][khalf][row n][64 cols], rows of 128 bytes, 16-byte chunk c stored at c ^ (n & 7).
+// Pieces 0-1: fp16 hi / lo (m = hi + lo, lo in fp16 subnormals).  Pieces 2-4: bf16 p0 + p1 + p2.
+__global__ void k_rotation_image(const float* __restrict__ m, uint16_t* __restrict__ image) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;     // over 128 x 128
+  if (idx >= kDim * kDim) return;
+  const int n = idx / kDim, k = idx % kDim;
+  const float v = m[idx];
+  const __half hi = __float2half_rn(v);
+  const __half lo = __float2half_rn(v - __half2float(hi));
+  const __nv_bfloat16 p0 = __float2bfloat16_rn(v);
+  const float r1 = v - __bfloat162float(p0);
+  const __nv_bfloat16 p1 = __float2bfloat16_rn(r1);
+  const __nv_bfloat16 p2 = __float2bfloat16_rn(r1 - __bfloat162float(p1));
+  const int khalf = k >> 6, kk = k & 63;
+  const int chunk = (kk >> 3) ^ (n & 7);
+  const int off = khalf * (kTileRows * 64) + n * 64 + chunk * 8 + (kk & 7);
+  const int piece = kTileRows * kDim;
+  image[off] = __half_as_ushort(hi);
+  image[piece + off] = __half_as_ushort(lo);
+  image[2 * piece + off] = __bfloat16_as_ushort(p0);
+  image[3 * piece + off] = __bfloat16_as_ushort(p1);
+  image[4 * piece + off] = __bfloat16_as_ushort(p2);
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static std::atomic<void*> cached{nullptr};
+  void* p = cached.load();
+  if (p == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    cached.store(fn);
+    p = fn;
+  }
+  return reinterpret_cast<EncodeTiledFn>(p);
+}
+
+bool force_simt() {
+  const char* e = getenv("TQ_FORCE_SIMT");
+  return e != nullptr && e[0] == '1';
+}
+
+}  // namespace
+
+size_t umma_rotation_image_bytes(int D) { return D == kDim ? (size_t)kImageBytes : 0; }
+
+int umma_prepare_rotation_image(const float* m, int D, void* image, cudaStream_t st) {
+  if (D != kDim) return TQ_EDIM;
+  k_rotation_image<<<(kDim * kDim + 255) / 256, 256, 0, st>>>(m, reinterpret_cast<uint16_t*>(image));
+  return check_launch();
+}
+
+bool umma_quantize_eligible(const TqQuantizeJob& j) {
+  if (force_simt()) return false;
+  if (j.rotation_image == nullptr || j.D != kDim || j.normalize != 1 || j.idx_mode != TQ_IDX_PACKED) return false;
+  if (j.x_dtype != TQ_F16 && j.x_dtype != TQ_BF16) return false;
+  if (j.B <= 0 || j.H <= 0 || j.S <= 0) return false;
+  if (j.B > 65535 || j.H > 65535 || j.S > (int64_t)1 << 30) return false;
+  if (((uintptr_t)j.x & 15u) || ((uintptr_t)j.idx_out & 15u) || ((uintptr_t)j.rotation_image & 15u)) return false;
+  if ((j.S > 1 && (j.stride_s % 8 != 0 || j.stride_s < kDim)) || (j.H > 1 && j.stride_h % 8 != 0) ||
+      (j.B > 1 && j.stride_b % 8 != 0))
+    return false;
+  if (j.stride_s < 0 || j.stride_h < 0 || j.stride_b < 0) return false;
+  const int64_t tiles = j.B * j.H * ((j.S + kTileRows - 1) / kTileRows);
+  return tiles < ((int64_t)1 << 30);
+}
+
+// Launch one persistent kernel over up to kMaxJobs eligible jobs (all of one input dtype).
+int umma_quantize(const TqQuantizeJob* jobs, int n_jobs, cudaStream_t st) {
+  EncodeTiledFn enc = encode_fn();
+  if (enc == nullptr) return TQ_ELAUNCH;
+  static thread_local UmmaQuantBatch batch;      // large: keep it off the stack
+  int done = 0;
+  while (done < n_jobs) {
+    const int take = (n_jobs - done) < kMaxJobs ? (n_jobs - done) : kMaxJobs;
+    int64_t tile_cursor = 0;
+    for (int i = 0; i < take; ++i) {
+      const TqQuantizeJob& j = jobs[done + i];
+      UmmaQuantJob& u = batch.jobs[i];
+      const int64_t tps = (j.S + kTileRows - 1) / kTileRows;
+      // size-1 dimensions get a harmless stride; TMA wants multiples of 16 bytes
+      const int64_t ss = j.S > 1 ? j.stride_s : kDim;
+      const int64_t sh = j.H > 1 ? j.stride_h : ss * j.S;
+      const int64_t sb = j.B > 1 ? j.stride_b : (sh > ss ? sh : ss) * (j.H > 1 ? j.H : j.S);
+      cuuint64_t dims[4] = {(cuuint64_t)kDim, (cuuint64_t)j.S, (cuuint64_t)j.H, (cuuint64_t)j.B};
+      cuuint64_t strides[3] = {(cuuint64_t)ss * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
+      cuuint32_t box[4] = {64, (cuuint32_t)kTileRows, 1, 1};
+      cuuint32_t estr[4] = {1, 1, 1, 1};
+      CUresult r = enc(&u.tmap, j.x_dtype == TQ_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                       const_cast<void*>(j.x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) { note_cuda_error(100000 + (int)r); return TQ_ELAUNCH; }
+      u.image = j.rotation_image;
+      u.codebook = j.codebook;
+      u.idx_out = reinterpret_cast<uint8_t*>(j.idx_out);
+      u.norms_out = j.norms_out;
+      u.S = j.S;
+      u.H = (int32_t)j.H;
+      u.tiles_per_slab = (int32_t)tps;
+      u.tile_begin = (int32_t)tile_cursor;
+      u.bits = j.bits;
+      u.a_bf16 = j.x_dtype == TQ_BF16;
+      u.pad_ = 0;
+      tile_cursor += tps * j.B * j.H;
+      if (tile_cursor >= ((int64_t)1 << 30)) return TQ_ETOOBIG;
+    }
+    batch.n_jobs = take;
+    batch.total_tiles = (int32_t)tile_cursor;
+    void* status_ptr = nullptr;
+    cudaGetSymbolAddress(&status_ptr, g_umma_status);
+    batch.status = reinterpret_cast<int32_t*>(status_ptr);
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = (int)(tile_cursor < sms ? tile_cursor : sms);
+    const bool bf16 = jobs[done].x_dtype == TQ_BF16;
+    const uint32_t smem = bf16 ? Cfg<true>::kSmemBytes : Cfg<false>::kSmemBytes;
+    cudaError_t e = bf16 ? cudaFuncSetAttribute(k_umma_quantize<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                         : cudaFuncSetAttribute(k_umma_quantize<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { note_cuda_error((int)e); return TQ_ELAUNCH; }
+    if (bf16) k_umma_quantize<true><<<grid, kThreads, smem, st>>>(batch);
+    else k_umma_quantize<false><<<grid, kThreads, smem, st>>>(batch);
+    int rc = check_launch();
+    if (rc != TQ_OK) return rc;
+    done += take;
+  }
+  return TQ_OK;
+}
+
+int umma_device_status() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_umma_status, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+}  // namespace tq

@@ -32,7 +32,8 @@ class QuantizeJob(C.Structure):
                 ("normalize", C.c_int32), ("B", C.c_int64), ("H", C.c_int64), ("S", C.c_int64),
                 ("stride_b", C.c_int64), ("stride_h", C.c_int64), ("stride_s", C.c_int64),
                 ("rotation_t", C.c_void_p), ("codebook", C.c_void_p), ("idx_mode", C.c_int32),
-                ("reserved", C.c_int32), ("idx_out", C.c_void_p), ("norms_out", C.c_void_p)]
+                ("reserved", C.c_int32), ("idx_out", C.c_void_p), ("norms_out", C.c_void_p),
+                ("rotation_image", C.c_void_p)]
 
 
 class DequantizeJob(C.Structure):
@@ -86,6 +87,11 @@ def lib():
     L.tq_launch_count.restype = i64
     L.tq_packed_row_bytes.argtypes = [i32, i32]
     L.tq_build_codebook.argtypes = [vp, i32, vp]
+    L.tq_rotation_image_bytes.restype = sz
+    L.tq_rotation_image_bytes.argtypes = [i32]
+    L.tq_prepare_rotation_image.argtypes = [vp, i32, vp, vp]
+    L.tq_prepare_rotation_image.restype = i32
+    L.tq_last_device_status.restype = i32
     L.tq_quantize_rotated.argtypes = [vp, i64, i32, i32, vp, i32, vp, vp]
     L.tq_quantize.argtypes = [C.POINTER(QuantizeJob), i32, vp]
     L.tq_dequantize.argtypes = [C.POINTER(DequantizeJob), i32, vp]
@@ -152,6 +158,25 @@ def codebook_block(centroids: torch.Tensor, bits: int) -> torch.Tensor:
     block = torch.empty(CODEBOOK_FLOATS, dtype=torch.float32)
     check(lib().tq_build_codebook(c.data_ptr(), bits, block.data_ptr()), "tq_build_codebook")
     return block
+
+
+def rotation_image(m: torch.Tensor):
+    """Tensor-core operand image of a (D, D) fp32 CUDA matrix, or None when there is no such path for D."""
+    if not m.is_cuda:
+        return None
+    D = m.shape[0]
+    nbytes = lib().tq_rotation_image_bytes(D)
+    if nbytes == 0:
+        return None
+    m = m.contiguous()
+    # over-allocate so that the image can start on a 1024-byte boundary
+    buf = torch.empty(nbytes + 1024, dtype=torch.uint8, device=m.device)
+    off = (-buf.data_ptr()) % 1024
+    img = buf[off:off + nbytes]
+    with torch.cuda.device(m.device):
+        check(lib().tq_prepare_rotation_image(m.data_ptr(), D, img.data_ptr(), stream_ptr(m.device)),
+              "tq_prepare_rotation_image")
+    return img
 
 
 def bhs_strides(t: torch.Tensor):

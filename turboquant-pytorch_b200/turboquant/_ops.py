@@ -19,7 +19,7 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def quantize_job(x: torch.Tensor, pi_t: torch.Tensor, codebook: torch.Tensor, bits: int, normalize: bool,
-                 idx_mode: int):
+                 idx_mode: int, image: Optional[torch.Tensor] = None):
     """Prepare one quantise job for a (B,H,S,D) tensor; returns (job, idx_out, norms_out, keepalive)."""
     N.require_cuda(x, "quantize")
     B, H, S, D = x.shape
@@ -35,7 +35,7 @@ def quantize_job(x: torch.Tensor, pi_t: torch.Tensor, codebook: torch.Tensor, bi
     job = N.QuantizeJob(x=x.data_ptr(), x_dtype=N.dtype_code(x), D=D, bits=bits, normalize=int(normalize),
                         B=B, H=H, S=S, stride_b=sb, stride_h=sh, stride_s=ss, rotation_t=pi_t.data_ptr(),
                         codebook=codebook.data_ptr(), idx_mode=idx_mode, reserved=0, idx_out=idx.data_ptr(),
-                        norms_out=_ptr(norms))
+                        norms_out=_ptr(norms), rotation_image=_ptr(image))
     return job, idx, norms, x
 
 

@@ -31,6 +31,7 @@ class MSECompressor:
         self.centroids = LloydMaxCodebook(head_dim, bits).centroids.to(device)
         self._pi_t = self.Pi.T.contiguous()
         self._cb = N.codebook_block(self.centroids, bits).to(device) if 1 <= bits <= 8 else None
+        self._img_q = N.rotation_image(self.Pi)          # tensor-core operand (None off-GPU or for other head_dims)
 
     def _need_bits(self):
         if self._cb is None:
@@ -42,7 +43,8 @@ class MSECompressor:
         B, H, S, D = states.shape
         if D != self.head_dim:
             raise ValueError(f"last dimension {D} != head_dim {self.head_dim}")
-        job, idx, norms, keep = _ops.quantize_job(states, self._pi_t, self._cb, self.bits, True, N.IDX_PACKED)
+        job, idx, norms, keep = _ops.quantize_job(states, self._pi_t, self._cb, self.bits, True, N.IDX_PACKED,
+                                                  image=self._img_q)
         ipb = 8 // self.bits
         result = {"idx_bytes": idx, "vec_norms": norms, "shape": (B, H, S, D), "idx_pad": (ipb - D % ipb) % ipb}
         return job, result, keep
