@@ -138,6 +138,8 @@ typedef struct {
   int64_t ostride_b, ostride_h, ostride_s;
   const float* rotation;  /* [dev] Pi, (D, D) row-major fp32: x_hat = c[idx] @ rotation      */
   const float* codebook;  /* [dev] 512-float block                                           */
+  const void* rotation_image; /* [dev] optional: tq_prepare_rotation_image(Pi^T) output; with it, head_dim
+                             128 and TQ_IDX_PACKED with norms run on the tensor cores            */
 } TqDequantizeJob;
 
 /* Replaces: MSECompressor.decompress turboquant/compressors_v3.py:83-105; with a

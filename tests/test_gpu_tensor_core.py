@@ -122,3 +122,75 @@ def test_nan_and_zero_rows_on_the_tensor_core_path():
     # an Inf coordinate meets both signs of the split rotation, so its norm comes out NaN here
     # (the FP32 path and the reference give Inf); the indices are 0 either way
     assert n[3].item() == 0 and torch.isnan(n[9]) and (torch.isinf(n[200]) or torch.isnan(n[200]))
+
+
+# ------------------------------------------------------------------ dequantize
+def _close_16bit(got, ref, dtype):
+    """fp16: within 2e-3 of the largest value.  bf16 cannot express 2e-3 (one ulp is 2^-8..2^-7
+    of a value), so there the bar is one bf16 ulp of the largest value, plus a mean error
+    below 2e-3 so that a systematic offset cannot hide in it."""
+    g, r = got.float().cpu(), ref.float().cpu()
+    worst = float((g - r).abs().max()) / float(r.abs().max())
+    if dtype == torch.float16:
+        return worst <= 2e-3
+    return worst <= 2.0 ** -7 and float((g - r).abs().mean()) <= 2e-3 * float(r.abs().mean())
+
+
+@pytest.mark.parametrize("bits", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_tensor_core_dequantize_fp32_matches_fp32_path_and_oracle(bits):
+    x = O.synthetic_kv((2, 3, 333, 128), torch.float16, seed=500 + bits)
+    comp = tq.MSECompressor(128, bits, seed=20 + bits, device=DEV)
+    assert comp._img_d is not None
+    c = comp.compress(x.to(DEV))
+    rec = comp.decompress(c)
+    ref = _simt(lambda: comp.decompress(c))
+    torch.cuda.synchronize()
+    assert N.lib().tq_last_device_status() == 0
+    assert rec.dtype == torch.float32 and rec.shape == (2, 3, 333, 128)
+    scale = float(ref.abs().max())
+    assert float((rec - ref).abs().max()) <= 1e-5 * scale
+    cent = O.lloyd_max(128, bits)[0]
+    want = O.mse_decompress({k: (v.cpu() if torch.is_tensor(v) else v) for k, v in c.items()}, comp.Pi.cpu(), cent, bits)
+    assert float((rec.cpu() - want).abs().max()) <= 1e-5 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bits,window", [(2, 0), (4, 0), (4, 37), (6, 16), (8, 128)])
+def test_tensor_core_decompress_kv_into_cache_dtype(dtype, bits, window):
+    keys = O.synthetic_kv((2, 2, 400, 128), dtype, seed=60 + bits)
+    vals = O.synthetic_kv((2, 2, 400, 128), dtype, seed=61 + bits)
+    codec = tq.TurboQuantV3(128, key_bits=bits, value_bits=max(bits - 2, 1), residual_window=window, layer_idx=7, n_layers=36,
+                            protected_layers=0, device=DEV)
+    ck, cv = codec.compress_kv(keys.to(DEV), vals.to(DEV))
+    rk, rv = codec.decompress_kv(ck, cv)
+    fk, fv = _simt(lambda: codec.decompress_kv(ck, cv))
+    torch.cuda.synchronize()
+    assert N.lib().tq_last_device_status() == 0
+    for got, ref, src in ((rk, fk, keys), (rv, fv, vals)):
+        assert got.dtype == dtype and got.shape == src.shape
+        assert _close_16bit(got, ref, dtype)
+        cut = 400 - window
+        assert torch.equal(got[:, :, cut:].cpu(), src[:, :, cut:])
+    # against the oracle end to end
+    ref = O.V3Oracle(128, key_bits=bits, value_bits=max(bits - 2, 1), residual_window=window, layer_idx=7, n_layers=36,
+                     protected_layers=0)
+    cpu = lambda d: {k: (({kk: (vv.cpu() if torch.is_tensor(vv) else vv) for kk, vv in v.items()} if isinstance(v, dict)
+                          else (v.cpu() if torch.is_tensor(v) else v))) for k, v in d.items()}
+    ok_, ov_ = ref.decompress_kv(cpu(ck), cpu(cv))
+    assert _close_16bit(rk, ok_, dtype) and _close_16bit(rv, ov_, dtype)
+
+
+def test_tensor_core_dequantize_many_layers_one_launch():
+    L = 10
+    codecs = [tq.TurboQuantV3(128, key_bits=4, value_bits=2, residual_window=0, layer_idx=l, n_layers=L, protected_layers=1,
+                              device=DEV) for l in range(L)]
+    keys = [O.synthetic_kv((1, 2, 700 + 128 * l, 128), torch.float16, 800 + l).to(DEV) for l in range(L)]
+    vals = [O.synthetic_kv((1, 2, 700 + 128 * l, 128), torch.float16, 900 + l).to(DEV) for l in range(L)]
+    packed = batched.compress_kv_layers(codecs, keys, vals)
+    outs = batched.decompress_kv_layers(codecs, packed)
+    refs = _simt(lambda: batched.decompress_kv_layers(codecs, packed))
+    torch.cuda.synchronize()
+    assert N.lib().tq_last_device_status() == 0
+    for l in range(L):
+        for got, ref in zip(outs[l], refs[l]):
+            assert float((got.float() - ref.float()).abs().max()) <= 2e-3 * float(ref.float().abs().max())

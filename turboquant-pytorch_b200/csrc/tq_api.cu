@@ -159,8 +159,20 @@ int tq_dequantize(const TqDequantizeJob* jobs, int n_jobs, void* stream) {
     if (j.B * j.H * j.S == 0) continue;
     if (j.idx == nullptr || j.rotation == nullptr || j.codebook == nullptr || j.out == nullptr) return TQ_ENULL;
   }
-  for (int i = 0; i < n_jobs; ++i) {
-    int rc = tq::simt_dequantize(jobs[i], (cudaStream_t)stream);
+  int i = 0;
+  while (i < n_jobs) {
+    if (jobs[i].B * jobs[i].H * jobs[i].S == 0) { ++i; continue; }
+    int rc;
+    if (tq::umma_dequantize_eligible(jobs[i])) {
+      const bool out32 = jobs[i].out_dtype == TQ_F32;
+      int k = i + 1;
+      while (k < n_jobs && (jobs[k].out_dtype == TQ_F32) == out32 && tq::umma_dequantize_eligible(jobs[k])) ++k;
+      rc = tq::umma_dequantize(jobs + i, k - i, (cudaStream_t)stream);
+      i = k;
+    } else {
+      rc = tq::simt_dequantize(jobs[i], (cudaStream_t)stream);
+      ++i;
+    }
     if (rc != TQ_OK) return rc;
   }
   return TQ_OK;

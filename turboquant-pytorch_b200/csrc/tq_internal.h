@@ -33,6 +33,8 @@ size_t umma_rotation_image_bytes(int D);
 int umma_prepare_rotation_image(const float* m, int D, void* image, cudaStream_t st);
 bool umma_quantize_eligible(const TqQuantizeJob& job);
 int umma_quantize(const TqQuantizeJob* jobs, int n_jobs, cudaStream_t st);
+bool umma_dequantize_eligible(const TqDequantizeJob& job);
+int umma_dequantize(const TqDequantizeJob* jobs, int n_jobs, cudaStream_t st);
 int umma_device_status();
 
 }  // namespace tq

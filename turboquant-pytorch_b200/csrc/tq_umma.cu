@@ -40,7 +40,7 @@ constexpr uint32_t kTileBytes = kTileRows * kDim * 2;  // 32768
 constexpr uint32_t kHalfBytes = kTileBytes / 2;        // one 64-column box
 constexpr uint32_t kImageBytes = 5 * kTileBytes;       // fp16 hi, lo; then bf16 p0, p1, p2
 constexpr int kMaxJobs = 96;
-constexpr uint32_t kSpinLimit = 1u << 22;              // bounded waits (each try_wait suspends for a while itself)
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // every mbarrier wait gives up after 2 s
 
 // shared memory map (offsets from a 1024-byte aligned base)
 template <bool BF16>
@@ -105,13 +105,22 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
-// Bounded wait: false when the limit ran out or another role aborted.
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false when the time limit ran out or another role aborted.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long start = global_ns();
+  for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 1023u) == 1023u && *abort_flag) return false;
+    if ((it & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_ns() - start > kWaitLimitNs) return false;
+    }
   }
-  return false;
 }
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
@@ -151,6 +160,7 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
+  __syncwarp();     // warp-collective load: all 32 lanes together
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -429,6 +439,319 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
   }
 }
 
+// ---------------------------------------------------------------- dequantize
+// unpack + centroid lookup + inverse rotation + rescale, head_dim 128, packed indices.
+// Each of NWG warpgroups owns one A buffer and one TMEM accumulator and alternates
+// between expanding a tile (packed indices -> fp16 centroid pieces written straight
+// into the swizzled K-major operand layout) and draining the previous result (TMEM ->
+// x norm -> cache dtype -> 16-byte stores).  Warp 1 issues the MMAs, warp 0 brings in
+// the rotation image when the job changes.  16-bit outputs need one pass (c_hi . Pi_hi,
+// error ~3e-4 of a 2e-3 budget); fp32 output takes three (hi.hi + lo.hi + hi.lo ~ 2^-21).
+struct alignas(16) UmmaDeqJob {
+  const uint8_t* idx;
+  const uint16_t* norms;
+  const void* image;         // image of Pi^T
+  const float* codebook;
+  void* out;
+  int64_t S;
+  int64_t os_b, os_h, os_s;  // output strides in elements
+  int32_t H;
+  int32_t tiles_per_slab;
+  int32_t tile_begin;
+  int32_t bits;
+  int32_t out_dtype;
+  int32_t pad_;
+};
+constexpr int kMaxDeqJobs = 192;
+struct UmmaDeqBatch {
+  int32_t n_jobs;
+  int32_t total_tiles;
+  int32_t* status;
+  UmmaDeqJob jobs[kMaxDeqJobs];
+};
+static_assert(sizeof(UmmaDeqBatch) < 32000, "kernel parameter space");
+
+template <bool OUT32>
+struct DCfg {
+  static constexpr int kWG = OUT32 ? 2 : 4;
+  static constexpr int kPiecesA = OUT32 ? 2 : 1;
+  static constexpr int kPiecesB = OUT32 ? 2 : 1;
+  static constexpr int kThreadsD = 64 + kWG * 128;
+  static constexpr uint32_t kOffA = 0;
+  static constexpr uint32_t kOffPi = kOffA + kWG * kPiecesA * kTileBytes;
+  static constexpr uint32_t kOffLut = kOffPi + kPiecesB * kTileBytes;          // kWG x 256 words
+  static constexpr uint32_t kOffBar = kOffLut + kWG * 1024;
+  static constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;
+};
+static_assert(DCfg<false>::kSmemBytes <= 232448 && DCfg<true>::kSmemBytes <= 232448, "shared memory budget");
+
+__device__ __forceinline__ int find_djob(const UmmaDeqBatch& b, int tile, int from) {
+  int j = from < 0 ? 0 : from;
+  while (j + 1 < b.n_jobs && tile >= b.jobs[j + 1].tile_begin) ++j;
+  return j;
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// Expand one row: G packed bytes -> 128 fp16 values per piece, 16-byte chunk q of k-half h
+// at  h*16384 + row*128 + ((q ^ (row & 7)) << 4).  lut[i] = {hi(c_i) | lo(c_i) << 16}.
+template <int BITS, int PIECES>
+__device__ __forceinline__ void expand_row(const uint8_t* __restrict__ packed, const uint32_t* lut, uint32_t a_stage,
+                                           int row) {
+  constexpr int IPB = 8 / BITS;
+  constexpr int G = kDim / IPB;                 // bytes per row: 16, 32, 64, 128
+  constexpr uint32_t MASK = (1u << BITS) - 1u;
+  const uint4* src = reinterpret_cast<const uint4*>(packed);
+#pragma unroll
+  for (int v = 0; v < G / 16; ++v) {
+    const uint4 raw = __ldg(src + v);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    constexpr int ELEMS = 16 * IPB;             // coordinates covered by these 16 bytes
+#pragma unroll
+    for (int q8 = 0; q8 < ELEMS / 8; ++q8) {    // one 16-byte operand chunk = 8 coordinates
+      uint32_t hi[4], lo[4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        uint32_t e2[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int e = q8 * 8 + p * 2 + u;     // coordinate within this 16-byte load
+          const int byte = e / IPB;
+          const int sh = 8 * (byte & 3) + BITS * (IPB - 1 - (e % IPB));
+          e2[u] = lut[(w[byte >> 2] >> sh) & MASK];
+        }
+        hi[p] = __byte_perm(e2[0], e2[1], 0x5410);
+        lo[p] = __byte_perm(e2[0], e2[1], 0x7632);
+      }
+      const int coord = v * ELEMS + q8 * 8;     // first coordinate of the chunk, 0..127
+      const int half = coord >> 6;
+      const int q = (coord & 63) >> 3;
+      const uint32_t dst = a_stage + half * kHalfBytes + row * 128 + ((q ^ (row & 7)) << 4);
+      st_shared_v4(dst, hi[0], hi[1], hi[2], hi[3]);
+      if constexpr (PIECES == 2) st_shared_v4(dst + kTileBytes, lo[0], lo[1], lo[2], lo[3]);
+    }
+  }
+}
+
+// The TMEM load is warp-collective: every lane of the warp must come through here, rows
+// past the end of a slab included; `valid` only guards the stores.
+template <int ODT>
+__device__ __forceinline__ void drain_row(uint32_t tacc, float nv, void* out_row, bool valid) {
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    float v[32];
+    tmem_ld32(tacc + c * 32, v);
+    if (!valid) continue;
+#pragma unroll
+    for (int e = 0; e < 32; ++e) v[e] *= nv;
+    if constexpr (ODT == TQ_F32) {
+      float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(out_row) + c * 32);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = make_float4(v[4 * e], v[4 * e + 1], v[4 * e + 2], v[4 * e + 3]);
+    } else {
+      uint32_t pk[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        if constexpr (ODT == TQ_F16) {
+          __half2 h = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+          pk[e] = *reinterpret_cast<uint32_t*>(&h);
+        } else {
+          __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+          pk[e] = *reinterpret_cast<uint32_t*>(&h);
+        }
+      }
+      uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out_row) + c * 32);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[e] = make_uint4(pk[4 * e], pk[4 * e + 1], pk[4 * e + 2], pk[4 * e + 3]);
+    }
+  }
+}
+
+template <bool OUT32>
+__global__ void __launch_bounds__(DCfg<OUT32>::kThreadsD, 1) k_umma_dequantize(const __grid_constant__ UmmaDeqBatch batch) {
+  using C = DCfg<OUT32>;
+  constexpr int kWG = C::kWG;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t a_smem = base + C::kOffA;
+  const uint32_t pi_smem = base + C::kOffPi;
+  uint32_t* lut_all = reinterpret_cast<uint32_t*>(gbase + C::kOffLut);
+  const uint32_t bar0 = base + C::kOffBar;
+  const uint32_t bar_full = bar0;                 // [kWG] A tile expanded
+  const uint32_t bar_tfull = bar0 + 8 * kWG;      // [kWG] accumulator ready
+  const uint32_t bar_pifull = bar_tfull + 8 * kWG;
+  const uint32_t bar_pifree = bar_pifull + 8;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + C::kOffBar + 200);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + C::kOffBar + 208);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total = batch.total_tiles;
+  const int t0 = (int)((int64_t)total * blockIdx.x / gridDim.x);
+  const int t1 = (int)((int64_t)total * (blockIdx.x + 1) / gridDim.x);
+  const int n_local = t1 - t0;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kWG; ++i) { mbar_init(bar_full + 8 * i, 1); mbar_init(bar_tfull + 8 * i, 1); }
+    mbar_init(bar_pifull, 1);
+    mbar_init(bar_pifree, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- rotation image loader
+    if (lane == 0) {
+      int cur_job = -1, pi_loads = 0;
+      bool ok = true;
+      for (int i = 0; i < n_local && ok; ++i) {
+        const int j = find_djob(batch, t0 + i, cur_job);
+        if (j == cur_job) continue;
+        if (pi_loads > 0) ok = mbar_wait(bar_pifree, (uint32_t)((pi_loads - 1) & 1), abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_pifull, C::kPiecesB * kTileBytes);
+        const uint8_t* img = reinterpret_cast<const uint8_t*>(batch.jobs[j].image);
+#pragma unroll
+        for (int p = 0; p < C::kPiecesB; ++p) bulk_load(pi_smem + p * kTileBytes, img + p * kTileBytes, kTileBytes, bar_pifull);
+        ++pi_loads;
+        cur_job = j;
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        if (batch.status != nullptr) atomicCAS(batch.status, 0, (4 << 16) | (int)blockIdx.x);
+      }
+      if (pi_loads > 0) mbar_wait(bar_pifull, (uint32_t)((pi_loads - 1) & 1), abort_flag);
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer
+    if (lane == 0) {
+      int cur_job = -1, pi_uses = 0;
+      bool ok = true;
+      const uint32_t idesc = idesc_f16(false);
+      for (int i = 0; i < n_local && ok; ++i) {
+        const int t = t0 + i;
+        const int j = find_djob(batch, t, cur_job);
+        if (j != cur_job) {
+          ok = mbar_wait(bar_pifull, (uint32_t)(pi_uses & 1), abort_flag);
+          if (!ok) break;
+          ++pi_uses;
+          cur_job = j;
+        }
+        const int g = i % kWG;
+        ok = mbar_wait(bar_full + 8 * g, (uint32_t)((i / kWG) & 1), abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(g * 128);
+        const uint32_t a_tile = a_smem + g * C::kPiecesA * kTileBytes;
+        // pass list: (A piece, B piece): hi.hi [, lo.hi, hi.lo]
+        constexpr int kPasses = OUT32 ? 3 : 1;
+#pragma unroll
+        for (int pass = 0; pass < kPasses; ++pass) {
+          const int pa = (pass == 1) ? 1 : 0;
+          const int pb = (pass == 2) ? 1 : 0;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t koff = (uint32_t)((k >> 2) * kHalfBytes + (k & 3) * 32);
+            const uint64_t adesc = smem_desc_sw128(a_tile + pa * kTileBytes + koff);
+            const uint64_t bdesc = smem_desc_sw128(pi_smem + pb * kTileBytes + koff);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (pass | k) != 0 ? 1u : 0u);
+          }
+        }
+        umma_commit(bar_tfull + 8 * g);
+        const int next_job = (i + 1 < n_local) ? find_djob(batch, t + 1, cur_job) : -1;
+        if (next_job != cur_job) umma_commit(bar_pifree);
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        if (batch.status != nullptr) atomicCAS(batch.status, 0, (5 << 16) | (int)blockIdx.x);
+      }
+    }
+  } else {
+    // ---- warpgroups: expand, then drain
+    const int ew = warp - 2;
+    const int wg = ew >> 2;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    uint32_t* lut = lut_all + wg * 256;
+    const int wg_tid = (ew & 3) * 32 + lane;
+    const uint32_t a_stage = a_smem + wg * C::kPiecesA * kTileBytes;
+    int cur_job = -1;
+    bool ok = true;
+    for (int i = wg; i < n_local && ok; i += kWG) {
+      const int t = t0 + i;
+      const int j = find_djob(batch, t, cur_job);
+      const UmmaDeqJob& job = batch.jobs[j];
+      if (j != cur_job) {
+        asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");
+        for (int e = wg_tid; e < 256; e += 128) {
+          const float c = __ldg(job.codebook + kCentroidOff + e);
+          const __half h = __float2half_rn(c);
+          const __half l = __float2half_rn(c - __half2float(h));
+          lut[e] = (uint32_t)__half_as_ushort(h) | ((uint32_t)__half_as_ushort(l) << 16);
+        }
+        asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");
+        cur_job = j;
+      }
+      const int lt = t - job.tile_begin;
+      const int slab = lt / job.tiles_per_slab;
+      const int64_t s_row = (int64_t)(lt - slab * job.tiles_per_slab) * kTileRows + row;
+      const bool valid = s_row < job.S;
+      const int64_t n = (int64_t)slab * job.S + s_row;
+      if (valid) {
+        const int ipb = 8 / job.bits;
+        const uint8_t* packed = job.idx + n * (int64_t)(kDim / ipb);
+        switch (job.bits) {
+          case 1: expand_row<1, C::kPiecesA>(packed, lut, a_stage, row); break;
+          case 2: expand_row<2, C::kPiecesA>(packed, lut, a_stage, row); break;
+          case 3: expand_row<3, C::kPiecesA>(packed, lut, a_stage, row); break;
+          case 4: expand_row<4, C::kPiecesA>(packed, lut, a_stage, row); break;
+          case 5: expand_row<5, C::kPiecesA>(packed, lut, a_stage, row); break;
+          case 6: expand_row<6, C::kPiecesA>(packed, lut, a_stage, row); break;
+          case 7: expand_row<7, C::kPiecesA>(packed, lut, a_stage, row); break;
+          default: expand_row<8, C::kPiecesA>(packed, lut, a_stage, row); break;
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");
+      if (wg_tid == 0) mbar_arrive(bar_full + 8 * wg);
+      ok = mbar_wait(bar_tfull + 8 * wg, (uint32_t)((i / kWG) & 1), abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(wg * 128);
+      {
+        const float nv = valid ? __half2float(__ushort_as_half(job.norms[n])) : 0.f;
+        const int hh = slab % job.H, bb = slab / job.H;
+        const int64_t off = (int64_t)bb * job.os_b + (int64_t)hh * job.os_h + s_row * job.os_s;
+        if constexpr (OUT32) {
+          drain_row<TQ_F32>(tacc, nv, reinterpret_cast<float*>(job.out) + off, valid);
+        } else {
+          if (job.out_dtype == TQ_F16) drain_row<TQ_F16>(tacc, nv, reinterpret_cast<uint16_t*>(job.out) + off, valid);
+          else drain_row<TQ_BF16>(tacc, nv, reinterpret_cast<uint16_t*>(job.out) + off, valid);
+        }
+      }
+      tc_fence_before();
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      if (batch.status != nullptr) atomicCAS(batch.status, 0, (6 << 16) | (int)blockIdx.x);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // ---------------------------------------------------------------- rotation image
 // image[piece][khalf][row n][64 cols], rows of 128 bytes, 16-byte chunk c stored at c ^ (n & 7).
 // Pieces 0-1: fp16 hi / lo (m = hi + lo, lo in fp16 subnormals).  Pieces 2-4: bf16 p0 + p1 + p2.
@@ -559,6 +882,71 @@ int umma_quantize(const TqQuantizeJob* jobs, int n_jobs, cudaStream_t st) {
     if (e != cudaSuccess) { note_cuda_error((int)e); return TQ_ELAUNCH; }
     if (bf16) k_umma_quantize<true><<<grid, kThreads, smem, st>>>(batch);
     else k_umma_quantize<false><<<grid, kThreads, smem, st>>>(batch);
+    int rc = check_launch();
+    if (rc != TQ_OK) return rc;
+    done += take;
+  }
+  return TQ_OK;
+}
+
+bool umma_dequantize_eligible(const TqDequantizeJob& j) {
+  if (force_simt()) return false;
+  if (j.rotation_image == nullptr || j.D != kDim || j.idx_mode != TQ_IDX_PACKED || j.norms == nullptr) return false;
+  if (j.B <= 0 || j.H <= 0 || j.S <= 0) return false;
+  if (((uintptr_t)j.idx & 15u) || ((uintptr_t)j.out & 15u) || ((uintptr_t)j.rotation_image & 15u)) return false;
+  const int64_t q = j.out_dtype == TQ_F32 ? 4 : 8;     // elements per 16 bytes
+  if (j.ostride_s % q != 0 || j.ostride_h % q != 0 || j.ostride_b % q != 0) return false;
+  const int64_t tiles = j.B * j.H * ((j.S + kTileRows - 1) / kTileRows);
+  return tiles < ((int64_t)1 << 30);
+}
+
+// One persistent launch over a run of eligible jobs that share the output class (fp32 vs 16-bit).
+int umma_dequantize(const TqDequantizeJob* jobs, int n_jobs, cudaStream_t st) {
+  static thread_local UmmaDeqBatch batch;
+  int done = 0;
+  while (done < n_jobs) {
+    const int take = (n_jobs - done) < kMaxDeqJobs ? (n_jobs - done) : kMaxDeqJobs;
+    int64_t tile_cursor = 0;
+    for (int i = 0; i < take; ++i) {
+      const TqDequantizeJob& j = jobs[done + i];
+      UmmaDeqJob& u = batch.jobs[i];
+      const int64_t tps = (j.S + kTileRows - 1) / kTileRows;
+      u.idx = reinterpret_cast<const uint8_t*>(j.idx);
+      u.norms = j.norms;
+      u.image = j.rotation_image;
+      u.codebook = j.codebook;
+      u.out = j.out;
+      u.S = j.S;
+      u.os_b = j.ostride_b; u.os_h = j.ostride_h; u.os_s = j.ostride_s;
+      u.H = (int32_t)j.H;
+      u.tiles_per_slab = (int32_t)tps;
+      u.tile_begin = (int32_t)tile_cursor;
+      u.bits = j.bits;
+      u.out_dtype = j.out_dtype;
+      u.pad_ = 0;
+      tile_cursor += tps * j.B * j.H;
+      if (tile_cursor >= ((int64_t)1 << 30)) return TQ_ETOOBIG;
+    }
+    batch.n_jobs = take;
+    batch.total_tiles = (int32_t)tile_cursor;
+    void* status_ptr = nullptr;
+    cudaGetSymbolAddress(&status_ptr, g_umma_status);
+    batch.status = reinterpret_cast<int32_t*>(status_ptr);
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = (int)(tile_cursor < sms ? tile_cursor : sms);
+    const bool out32 = jobs[done].out_dtype == TQ_F32;
+    cudaError_t e;
+    if (out32) {
+      e = cudaFuncSetAttribute(k_umma_dequantize<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DCfg<true>::kSmemBytes);
+      if (e != cudaSuccess) { note_cuda_error((int)e); return TQ_ELAUNCH; }
+      k_umma_dequantize<true><<<grid, DCfg<true>::kThreadsD, DCfg<true>::kSmemBytes, st>>>(batch);
+    } else {
+      e = cudaFuncSetAttribute(k_umma_dequantize<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DCfg<false>::kSmemBytes);
+      if (e != cudaSuccess) { note_cuda_error((int)e); return TQ_ELAUNCH; }
+      k_umma_dequantize<false><<<grid, DCfg<false>::kThreadsD, DCfg<false>::kSmemBytes, st>>>(batch);
+    }
     int rc = check_launch();
     if (rc != TQ_OK) return rc;
     done += take;

@@ -40,7 +40,7 @@ class DequantizeJob(C.Structure):
     _fields_ = [("idx", C.c_void_p), ("norms", C.c_void_p), ("idx_mode", C.c_int32), ("D", C.c_int32),
                 ("bits", C.c_int32), ("out_dtype", C.c_int32), ("B", C.c_int64), ("H", C.c_int64), ("S", C.c_int64),
                 ("out", C.c_void_p), ("ostride_b", C.c_int64), ("ostride_h", C.c_int64), ("ostride_s", C.c_int64),
-                ("rotation", C.c_void_p), ("codebook", C.c_void_p)]
+                ("rotation", C.c_void_p), ("codebook", C.c_void_p), ("rotation_image", C.c_void_p)]
 
 
 class ScoreJob(C.Structure):

@@ -46,7 +46,7 @@ def run_quantize(jobs: Sequence[N.QuantizeJob], device):
 
 
 def dequantize_job(idx: torch.Tensor, norms: Optional[torch.Tensor], shape, pi: torch.Tensor, codebook: torch.Tensor,
-                   bits: int, idx_mode: int, out: torch.Tensor):
+                   bits: int, idx_mode: int, out: torch.Tensor, image: Optional[torch.Tensor] = None):
     """One dequantise job writing into `out`, a (B,H,S,D) tensor or strided view with unit last stride."""
     N.require_cuda(idx, "dequantize")
     B, H, S, D = shape
@@ -58,7 +58,7 @@ def dequantize_job(idx: torch.Tensor, norms: Optional[torch.Tensor], shape, pi: 
     job = N.DequantizeJob(idx=idx.data_ptr(), norms=_ptr(norms), idx_mode=idx_mode, D=D, bits=bits,
                           out_dtype=N.dtype_code(out), B=B, H=H, S=S, out=out.data_ptr(), ostride_b=out.stride(0),
                           ostride_h=out.stride(1), ostride_s=out.stride(2), rotation=pi.data_ptr(),
-                          codebook=codebook.data_ptr())
+                          codebook=codebook.data_ptr(), rotation_image=_ptr(image))
     return job, (idx, norms)
 
 

@@ -31,7 +31,8 @@ class MSECompressor:
         self.centroids = LloydMaxCodebook(head_dim, bits).centroids.to(device)
         self._pi_t = self.Pi.T.contiguous()
         self._cb = N.codebook_block(self.centroids, bits).to(device) if 1 <= bits <= 8 else None
-        self._img_q = N.rotation_image(self.Pi)          # tensor-core operand (None off-GPU or for other head_dims)
+        self._img_q = N.rotation_image(self.Pi)          # tensor-core operands (None off-GPU or for other head_dims)
+        self._img_d = N.rotation_image(self._pi_t)
 
     def _need_bits(self):
         if self._cb is None:
@@ -52,7 +53,7 @@ class MSECompressor:
     def decompress_job(self, compressed: dict, out: torch.Tensor):
         self._need_bits()
         return _ops.dequantize_job(compressed["idx_bytes"], compressed["vec_norms"], compressed["shape"], self.Pi,
-                                   self._cb, self.bits, N.IDX_PACKED, out)
+                                   self._cb, self.bits, N.IDX_PACKED, out, image=self._img_d)
 
     @torch.no_grad()
     def compress(self, states: torch.Tensor) -> dict:
