@@ -187,20 +187,21 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    plan = batched.CachePlan(codecs, keys, vals)       # static buffers: one library call per phase
+
     def one_step(ev=None):
         flush.zero_()
         if ev:
             ev[0].record()
-        packed = batched.compress_kv_layers(codecs, keys, vals)
+        plan.compress()
         if ev:
             ev[1].record()
         flush.zero_()
         if ev:
             ev[2].record()
-        outs = batched.decompress_kv_layers(codecs, packed)
+        plan.decompress()
         if ev:
             ev[3].record()
-        return packed, outs
 
     for _ in range(args.warmup):
         one_step()
@@ -227,11 +228,12 @@ def main():
     e2e_steps = max(1, min(args.steps, 5))
 
     def e2e_step():
-        dk = [k.to(dev, non_blocking=True) for k in h_keys]
-        dv = [v.to(dev, non_blocking=True) for v in h_vals]
-        packed = batched.compress_kv_layers(codecs, dk, dv)
-        outs = batched.decompress_kv_layers(codecs, packed)
-        for l, (rk, rv) in enumerate(outs):
+        for l in range(n_layers):
+            keys[l].copy_(h_keys[l], non_blocking=True)
+            vals[l].copy_(h_vals[l], non_blocking=True)
+        plan.compress()
+        plan.decompress()
+        for l, (rk, rv) in enumerate(plan.reconstructed):
             h_out_k[l].copy_(rk, non_blocking=True)
             h_out_v[l].copy_(rv, non_blocking=True)
 
@@ -267,7 +269,7 @@ def main():
     out = {
         "metric": METRIC, "value": world * vectors_per_step * args.steps / t_all, "unit": "vectors/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_all / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "layers_per_gpu": n_layers, "units_per_gpu": n_layers * KV_HEADS,
                    "vectors_per_step_per_gpu": vectors_per_step,
                    "l2": "a 256 MiB buffer is overwritten before each phase (outside the event-timed intervals); "
@@ -282,7 +284,7 @@ def main():
         "e2e": {"value": world * vectors_per_step * e2e_steps / t_e2e, "unit": "vectors/s",
                 "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes, "steps": e2e_steps,
                 "ms_per_step": 1e3 * t_e2e / e2e_steps,
-                "what": "pinned host fp16 K,V -> device -> compress_kv_layers -> decompress_kv_layers -> pinned host fp16 K,V"},
+                "what": "pinned host fp16 K,V -> device -> CachePlan.compress -> CachePlan.decompress -> pinned host fp16 K,V"},
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
     }

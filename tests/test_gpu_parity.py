@@ -407,3 +407,25 @@ def test_v1_classes_against_golden():
     vals = cache.get_values()
     assert vals.shape == z["cache_values"].shape
     assert float(((vals.cpu() - torch.from_numpy(z["cache_values"])) ** 2).mean()) < 1e-3
+
+
+def test_cache_plan_equals_per_layer_calls_and_can_rerun():
+    L = 4
+    codecs = [tq.TurboQuantV3(128, key_bits=4, value_bits=2, residual_window=16, layer_idx=l, n_layers=L, protected_layers=1,
+                              device=DEV) for l in range(L)]
+    keys = [O.synthetic_kv((1, 2, 300, 128), torch.float16, 700 + l).to(DEV) for l in range(L)]
+    vals = [O.synthetic_kv((1, 2, 300, 128), torch.float16, 750 + l).to(DEV) for l in range(L)]
+    plan = batched.CachePlan(codecs, keys, vals)
+    for _ in range(2):                      # the second pass overwrites the same buffers
+        packed = plan.compress()
+        outs = plan.decompress()
+    for l in range(L):
+        ck, cv = codecs[l].compress_kv(keys[l], vals[l])
+        assert torch.equal(packed[l][0]["compressed"]["idx_bytes"], ck["compressed"]["idx_bytes"])
+        assert torch.equal(packed[l][1]["compressed"]["vec_norms"], cv["compressed"]["vec_norms"])
+        rk, rv = codecs[l].decompress_kv(ck, cv)
+        assert torch.equal(outs[l][0], rk) and torch.equal(outs[l][1], rv)
+    keys[0].mul_(0.5)                        # inputs changed in place: window must be refreshed by the caller
+    plan.compress(); plan.refresh_window(); plan.decompress()
+    rk, _ = codecs[0].decompress_kv(*codecs[0].compress_kv(keys[0], vals[0]))
+    assert torch.equal(plan.reconstructed[0][0], rk)

@@ -49,6 +49,72 @@ def decompress_kv_layers(codecs: Sequence[TurboQuantV3], compressed: Sequence[tu
     return results
 
 
+class CachePlan:
+    """Static-buffer plan for one whole KV cache (all layers, K and V).
+
+    Built once for fixed input tensors: packed outputs, reconstruction outputs and the job
+    arrays handed to the C ABI are allocated here, so compress() and decompress() are one
+    library call each with no per-call allocation or Python work per layer -- the form a
+    serving engine with preallocated cache buffers uses.  Results equal those of the
+    per-layer TurboQuantV3 calls on the same tensors.
+    """
+
+    def __init__(self, codecs: Sequence[TurboQuantV3], keys: Sequence[torch.Tensor], values: Sequence[torch.Tensor]):
+        from . import _native as N
+        self.device = keys[0].device
+        self._keep = []
+        qjobs, self.compressed = [], []
+        for codec, k, v in zip(codecs, keys, values):
+            j, res, ka = codec.compress_jobs(k, v)
+            qjobs.extend(j)
+            self.compressed.append(res)
+            self._keep.append(ka)
+        djobs, self.reconstructed = [], []
+        for codec, (ck, cv) in zip(codecs, self.compressed):
+            if ck["compressed"] is None:
+                self.reconstructed.append((ck["fp16"], cv["fp16"]))
+                continue
+            j, outs, ka = codec.decompress_jobs(ck, cv)
+            djobs.extend(j)
+            self.reconstructed.append(outs)
+            self._keep.append(ka)
+        self._n_q, self._n_d = len(qjobs), len(djobs)
+        self._qarr = (N.QuantizeJob * max(self._n_q, 1))(*qjobs)
+        self._darr = (N.DequantizeJob * max(self._n_d, 1))(*djobs)
+        self._lib = N.lib()
+        self._check = N.check
+        self._stream = N.stream_ptr
+
+    @torch.no_grad()
+    def compress(self):
+        """Quantise + pack every layer into the plan's packed buffers (self.compressed)."""
+        if self._n_q:
+            with torch.cuda.device(self.device):
+                self._check(self._lib.tq_quantize(self._qarr, self._n_q, self._stream(self.device)), "tq_quantize")
+        return self.compressed
+
+    @torch.no_grad()
+    def decompress(self):
+        """Unpack + dequantise every layer into the plan's output buffers (self.reconstructed).
+
+        The residual-window tokens were copied into the outputs when the plan was built; call
+        refresh_window() if the input tensors changed since."""
+        if self._n_d:
+            with torch.cuda.device(self.device):
+                self._check(self._lib.tq_dequantize(self._darr, self._n_d, self._stream(self.device)), "tq_dequantize")
+        return self.reconstructed
+
+    @torch.no_grad()
+    def refresh_window(self):
+        for (ck, cv), outs in zip(self.compressed, self.reconstructed):
+            if ck["compressed"] is None:
+                continue
+            for comp, full in ((ck, outs[0]), (cv, outs[1])):
+                cut = comp["split_at"]
+                if full.shape[2] > cut:
+                    full[:, :, cut:, :].copy_(comp["fp16"])
+
+
 def shard_units(n_layers: int, n_kv_heads: int, rank: int, world: int):
     """(layer, kv_head) units owned by `rank`: contiguous blocks of the layer-major unit list.
 
