@@ -151,6 +151,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per rank (smaller values are for profiling only)")
+    ap.add_argument("--key-bits", type=int, default=KEY_BITS, help="profiling only; the headline workload is K4")
+    ap.add_argument("--value-bits", type=int, default=VALUE_BITS, help="profiling only; the headline workload is V2")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -172,12 +174,13 @@ def main():
     lib = _native.lib()
     n_layers = args.layers
 
-    codecs = [tq.TurboQuantV3(HEAD_DIM, key_bits=KEY_BITS, value_bits=VALUE_BITS, residual_window=0, layer_idx=l,
+    kb, vb = args.key_bits, args.value_bits
+    codecs = [tq.TurboQuantV3(HEAD_DIM, key_bits=kb, value_bits=vb, residual_window=0, layer_idx=l,
                               n_layers=LAYERS, protected_layers=0, device=dev) for l in range(n_layers)]
     keys = [synthetic_layer(dev, 20000 + 100000 * rank + l) for l in range(n_layers)]
     vals = [synthetic_layer(dev, 25000 + 100000 * rank + l) for l in range(n_layers)]
     vectors_per_step = 2 * n_layers * KV_HEADS * SEQ
-    bytes_q = n_layers * KV_HEADS * SEQ * (algorithmic_bytes_per_vector(KEY_BITS) + algorithmic_bytes_per_vector(VALUE_BITS))
+    bytes_q = n_layers * KV_HEADS * SEQ * (algorithmic_bytes_per_vector(kb) + algorithmic_bytes_per_vector(vb))
     bytes_d = bytes_q
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # larger than the 126 MB L2
 

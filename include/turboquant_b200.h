@@ -53,15 +53,23 @@ enum {
 };
 
 #define TQ_MAX_DIM 256
-#define TQ_CODEBOOK_FLOATS 512
-/* A codebook block is 512 floats on the device: [0,L) centroids ascending,
- * [256, 256+L-1) decision thresholds, every other slot +inf.  Threshold k is
+#define TQ_CODEBOOK_FLOATS 528
+/* A codebook block is 528 floats on the device: [0,L) centroids ascending,
+ * [256, 256+L-1) decision thresholds, every other slot below 512 +inf, and
+ * [512,528) the parameters of the search shortcut (below).  Threshold k is
  * the largest fp32 y for which fl|y-c_k| <= fl|y-c_(k+1)|, so that
  * index(y) = #{k : y > threshold_k} equals the first-minimum argmin over
  * |y - c| evaluated in fp32 (turboquant/compressors_v3.py:60-61).  The identity
  * holds while ulp(y) is far below the centroid spacing (|y| < 1024 for every
  * codebook of head_dim 64..256; rotated unit vectors have |y| <= 1); beyond
- * that fp32 differences tie and the argmin itself stops being monotone.       */
+ * that fp32 differences tie and the argmin itself stops being monotone.
+ *
+ * Search shortcut (slots 512..): [512] = 1.0 when valid, [513] = s, [514..516] =
+ * c1, c2, c3.  With t = sat(y*s + 0.5) and e = round(t*(c1 + t*(c2 + t*c3))) the
+ * host has verified, in the same fp32 arithmetic, that the exact index is e or
+ * e+1 for every y, so index(y) = e + (y > threshold_e): one table look-up instead
+ * of a binary search, with the same result.  Built for up to 31 thresholds; when
+ * no cubic passes the check the slot [512] is 0 and kernels search.            */
 
 int tq_version(void);
 const char* tq_strerror(int code);
@@ -76,9 +84,9 @@ int64_t tq_launch_count(void);
  * Replaces: turboquant/compressors_v3.py:64-69 and :112-113.                  */
 int tq_packed_row_bytes(int D, int bits);
 
-/* Fill a 512-float codebook block [host] from L = 2^bits ascending centroids
+/* Fill a TQ_CODEBOOK_FLOATS codebook block [host] from L = 2^bits ascending centroids
  * [host].  Replaces the argmin rule of turboquant/compressors_v3.py:60-61.    */
-int tq_build_codebook(const float* centroids, int bits, float* block512);
+int tq_build_codebook(const float* centroids, int bits, float* block);
 
 /* Tensor-core operand image of a (D, D) row-major fp32 matrix m [dev]: two fp16 pieces
  * (m = hi + lo), K-major, 128-byte swizzled, tq_rotation_image_bytes(D) bytes (0 when D
@@ -108,7 +116,7 @@ typedef struct {
   int64_t B, H, S;        /* vector count = B*H*S                                            */
   int64_t stride_b, stride_h, stride_s;   /* in elements                                     */
   const float* rotation_t;/* [dev] Pi^T, (D, D) row-major fp32: y = x @ rotation_t           */
-  const float* codebook;  /* [dev] 512-float block                                           */
+  const float* codebook;  /* [dev] codebook block                                            */
   int32_t idx_mode;       /* TQ_IDX_*                                                        */
   int32_t reserved;
   void* idx_out;          /* [dev] (B*H*S, row) contiguous                                   */
@@ -137,7 +145,7 @@ typedef struct {
   void* out;              /* [dev] element (b,h,s,d) at out[b*ostride_b + h*ostride_h + s*ostride_s + d] */
   int64_t ostride_b, ostride_h, ostride_s;
   const float* rotation;  /* [dev] Pi, (D, D) row-major fp32: x_hat = c[idx] @ rotation      */
-  const float* codebook;  /* [dev] 512-float block                                           */
+  const float* codebook;  /* [dev] codebook block                                            */
   const void* rotation_image; /* [dev] optional: tq_prepare_rotation_image(Pi^T) output; with it, head_dim
                              128 and TQ_IDX_PACKED with norms run on the tensor cores            */
 } TqDequantizeJob;

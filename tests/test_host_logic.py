@@ -82,7 +82,7 @@ def test_thresholds_reproduce_fp32_argmin(d):
         block = N.codebook_block(torch.from_numpy(c), bits).numpy()
         L = 2 ** bits
         thr = block[256:256 + L - 1]
-        assert np.array_equal(block[:L], c) and np.all(np.isinf(block[L:256])) and np.all(np.isinf(block[256 + L - 1:]))
+        assert np.array_equal(block[:L], c) and np.all(np.isinf(block[L:256])) and np.all(np.isinf(block[256 + L - 1:512]))
         assert np.all(np.diff(thr) > 0)
         assert np.allclose(thr, z[f"b_{d}_{bits}"], atol=1e-7)
         # every float within +-16 ulp of each threshold, plus random draws and specials
@@ -193,3 +193,26 @@ def test_shard_units_partition():
         assert sorted(seen) == [(l, h) for l in range(36) for h in range(2)]
         sizes = [len(batched.shard_units(36, 2, r, world)) for r in range(world)]
         assert max(sizes) - min(sizes) <= 1
+
+
+def test_search_shortcut_parameters_bracket_the_exact_index():
+    """index = e + (y > thr[e]) needs the exact index to be e or e+1 for every y."""
+    z = load_golden("codebooks.npz")
+    rng = np.random.default_rng(0)
+    for d in (64, 128, 256):
+        for bits in range(1, 9):
+            block = N.codebook_block(torch.from_numpy(z[f"c_{d}_{bits}"]), bits).numpy().astype(np.float64)
+            n = 2 ** bits - 1
+            if bits > 5:
+                assert block[512] == 0.0          # more thresholds than lanes: kernels search instead
+                continue
+            assert block[512] == 1.0, (d, bits)
+            s, c1, c2, c3 = block[513:517]
+            thr = block[256:256 + n]
+            y = np.concatenate([rng.normal(0, 1 / np.sqrt(d), 50000), np.linspace(-1, 1, 20001), thr,
+                                np.nextafter(thr.astype(np.float32), np.float32(np.inf)).astype(np.float64)])
+            t = np.clip(y * s + 0.5, 0.0, 1.0)
+            e = np.rint(t * (c1 + t * (c2 + t * c3)))
+            exact = (y[:, None] > thr[None, :]).sum(axis=1)
+            assert np.all((e == exact) | (e + 1 == exact)), (d, bits)
+            assert e.min() >= 0 and e.max() <= 31

@@ -30,6 +30,95 @@ inline bool prefers_lower(float y, float a, float b) {
   return fabsf(da) <= fabsf(db);
 }
 
+// ---- search shortcut --------------------------------------------------------------
+// e(y) exactly as the kernels compute it (fp32 fma, saturate, round to nearest even).
+inline int shortcut_e(float y, float s, float c1, float c2, float c3) {
+  float t = fmaf(y, s, 0.5f);
+  if (!(t > 0.f)) t = 0.f;          // NaN -> 0, like a saturating fma
+  if (t > 1.f) t = 1.f;
+  float q = fmaf(c3, t, c2);
+  q = fmaf(q, t, c1);
+  const float u = fmaf(q, t, 8388608.0f);
+  int32_t bits;
+  memcpy(&bits, &u, 4);
+  return bits - 0x4B000000;
+}
+
+inline int exact_index(float y, const float* thr, int n) {
+  int c = 0;
+  for (int k = 0; k < n; ++k) c += (y > thr[k]) ? 1 : 0;
+  return c;
+}
+
+// Least-squares cubic through the origin mapping the thresholds to k + 1/2, then an
+// exhaustive check of "exact index is e or e+1" around every threshold and on a grid.
+void fit_shortcut(float* block, int n) {
+  for (int i = 512; i < TQ_CODEBOOK_FLOATS; ++i) block[i] = 0.f;
+  if (n < 1 || n > 31) return;
+  const float* thr = block + 256;
+  const double lim = fmax(fabs((double)thr[0]), fabs((double)thr[n - 1])) * 1.001 + 1e-12;
+  const float s = (float)(0.5 / lim);
+  // basis t, t^2, t^3 ; target k + 0.5 - 0.5 = k  (the constant 1/2 is the rounding offset)
+  double ata[3][3] = {{0}}, atb[3] = {0};
+  const int deg = n >= 3 ? 3 : n;        // fewer thresholds than coefficients: lower degree
+  for (int k = 0; k < n; ++k) {
+    const double t = (double)thr[k] * (double)s + 0.5;
+    const double b[3] = {t, t * t, t * t * t};
+    for (int i = 0; i < deg; ++i) {
+      for (int j = 0; j < deg; ++j) ata[i][j] += b[i] * b[j];
+      atb[i] += b[i] * (double)k;
+    }
+  }
+  double c[3] = {0, 0, 0};
+  // Gaussian elimination on the deg x deg normal equations (with a tiny ridge)
+  double m[3][4];
+  for (int i = 0; i < deg; ++i) {
+    for (int j = 0; j < deg; ++j) m[i][j] = ata[i][j] + (i == j ? 1e-12 : 0.0);
+    m[i][deg] = atb[i];
+  }
+  for (int i = 0; i < deg; ++i) {
+    int piv = i;
+    for (int r = i + 1; r < deg; ++r) if (fabs(m[r][i]) > fabs(m[piv][i])) piv = r;
+    for (int j = 0; j <= deg; ++j) { double tmp = m[i][j]; m[i][j] = m[piv][j]; m[piv][j] = tmp; }
+    if (fabs(m[i][i]) < 1e-300) return;
+    for (int r = i + 1; r < deg; ++r) {
+      const double f = m[r][i] / m[i][i];
+      for (int j = i; j <= deg; ++j) m[r][j] -= f * m[i][j];
+    }
+  }
+  for (int i = deg - 1; i >= 0; --i) {
+    double acc = m[i][deg];
+    for (int j = i + 1; j < deg; ++j) acc -= m[i][j] * c[j];
+    c[i] = acc / m[i][i];
+  }
+  const float c1 = (float)c[0], c2 = (float)c[1], c3 = (float)c[2];
+  auto ok_at = [&](float y) {
+    const int e = shortcut_e(y, s, c1, c2, c3);
+    const int i = exact_index(y, thr, n);
+    return e >= 0 && e <= 31 && (e == i || e + 1 == i) && (e < n || i == e);
+  };
+  for (int k = 0; k < n; ++k) {
+    float y = thr[k];
+    for (int step = 0; step < 4; ++step) y = nextafterf(y, -INFINITY);
+    for (int step = 0; step < 9; ++step) {
+      if (!ok_at(y)) return;
+      y = nextafterf(y, INFINITY);
+    }
+  }
+  const int grid = 1 << 16;
+  for (int g = 0; g <= grid; ++g) {
+    const float y = (float)(-1.25 + 2.5 * (double)g / grid);
+    if (!ok_at(y)) return;
+  }
+  const float specials[] = {0.f, -0.f, 1.f, -1.f, 100.f, -100.f, 1000.f, -1000.f, INFINITY, -INFINITY, NAN};
+  for (float y : specials) if (!ok_at(y)) return;
+  block[512] = 1.f;
+  block[513] = s;
+  block[514] = c1;
+  block[515] = c2;
+  block[516] = c3;
+}
+
 int check_common(int D, int bits) {
   if (bits < 1 || bits > 8) return TQ_EBITS;
   if (D < 1 || D > TQ_MAX_DIM) return TQ_EDIM;
@@ -89,6 +178,7 @@ int tq_build_codebook(const float* centroids, int bits, float* block) {
     }
     block[256 + k] = ord2f((int32_t)lo);
   }
+  fit_shortcut(block, L - 1);
   return TQ_OK;
 }
 

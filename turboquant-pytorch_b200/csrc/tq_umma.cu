@@ -176,6 +176,49 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Asynchronous form: issue now, consume after tmem_wait32 on the same registers.  The wait
+// lists the registers as read-write operands so that no use of them can move above it.
+__device__ __forceinline__ void tmem_issue32(uint32_t taddr, uint32_t (&r)[32]) {
+  __syncwarp();
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait32(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_issue16(uint32_t taddr, uint32_t (&r)[16]) {
+  __syncwarp();
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait16(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
+
 // K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
   uint64_t lo = (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16);
@@ -248,6 +291,105 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tmem_acc, const float* th
         *reinterpret_cast<uint4*>(idx_row + c * 32 + 16) = make_uint4(words[4], words[5], words[6], words[7]);
       }
     }
+  }
+}
+
+// Search shortcut (see the codebook block): one cubic, one lane look-up of the candidate
+// threshold, one compare.  Arithmetic is kept on the FMA pipe: the index is built as a
+// float next to 2^23 and shifted into the packed word by an integer multiply-add; the
+// 2^23 bit patterns that ride along are removed once per word as a constant.
+struct Shortcut {
+  float s, c1, c2, c3;
+  float thr_lane;      // threshold[lane] (+inf past the last one)
+};
+
+// CH coordinates (16 here) per step: the loop body stays small enough to live in the
+// instruction cache while four warps per scheduler run it out of phase.
+template <int BITS, int CH>
+__device__ __forceinline__ void quant_chunk_fast(const uint32_t (&raw)[CH], float inv, const Shortcut& sc, uint8_t* dst,
+                                                 bool valid) {
+  constexpr int IPB = 8 / BITS;
+  constexpr int BYTES = CH / IPB;               // packed bytes for CH coordinates
+  constexpr int WORDS = BYTES >= 4 ? BYTES / 4 : 1;
+  constexpr uint32_t kMagicBits = 0x4B000000u;  // 2^23
+  uint32_t acc[WORDS];
+#pragma unroll
+  for (int w = 0; w < WORDS; ++w) acc[w] = 0u;
+#pragma unroll
+  for (int e = 0; e < CH; ++e) {
+    const float y = __uint_as_float(raw[e]) * inv;
+    const float t = __saturatef(fmaf(y, sc.s, 0.5f));
+    float q = fmaf(sc.c3, t, sc.c2);
+    q = fmaf(q, t, sc.c1);
+    const float u = fmaf(q, t, 8388608.0f);
+    const float thr = __shfl_sync(0xffffffffu, sc.thr_lane, __float_as_int(u));
+    const float ui = u + ((y > thr) ? 1.0f : 0.0f);
+    const int byte = e / IPB;
+    const int shift = 8 * (byte & 3) + BITS * (IPB - 1 - (e % IPB));
+    acc[byte >> 2] = __float_as_uint(ui) * (1u << shift) + acc[byte >> 2];
+  }
+  // remove the 2^23 bit patterns that rode along: sum(magic << shift) mod 2^32 per word
+#pragma unroll
+  for (int w = 0; w < WORDS; ++w) {
+    uint32_t k = 0u;
+#pragma unroll
+    for (int e = 0; e < CH; ++e) {
+      const int byte = e / IPB;
+      if ((byte >> 2) == w) k += kMagicBits << (8 * (byte & 3) + BITS * (IPB - 1 - (e % IPB)));
+    }
+    acc[w] -= k;
+  }
+  if (valid) {
+    if constexpr (BYTES == 2) {
+      *reinterpret_cast<uint16_t*>(dst) = (uint16_t)acc[0];
+    } else if constexpr (BYTES == 4) {
+      *reinterpret_cast<uint32_t*>(dst) = acc[0];
+    } else if constexpr (BYTES == 8) {
+      *reinterpret_cast<uint2*>(dst) = make_uint2(acc[0], acc[1]);
+    } else {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(acc[0], acc[1], acc[2], acc[3]);
+    }
+  }
+}
+
+template <int CH>
+__device__ __forceinline__ float ssq_chunk(const uint32_t (&raw)[CH], float ssq) {
+#pragma unroll
+  for (int e = 0; e < CH; ++e) {
+    const float v = __uint_as_float(raw[e]);
+    ssq = fmaf(v, v, ssq);
+  }
+  return ssq;
+}
+
+// Two register buffers alternate so that a TMEM load is always in flight behind the math;
+// the loops stay rolled (two inlined copies of the step body, one per buffer).
+template <int BITS>
+__device__ __forceinline__ void epilogue_tile_fast(uint32_t tacc, const Shortcut& sc, uint8_t* idx_row,
+                                                   uint16_t* norm_ptr, bool valid) {
+  constexpr int CH = 16;
+  constexpr int STEPS = kDim / CH;               // 8
+  constexpr int BYTES = CH / (8 / BITS);
+  uint32_t a[CH], b[CH];
+  float ssq = 0.f;
+  tmem_issue16(tacc, a);
+#pragma unroll 1
+  for (int c = 0; c < STEPS; c += 2) {
+    tmem_wait16(a); tmem_issue16(tacc + (c + 1) * CH, b);
+    ssq = ssq_chunk<CH>(a, ssq);
+    tmem_wait16(b); tmem_issue16(tacc + ((c + 2) & (STEPS - 1)) * CH, a);   // wraps to step 0 for the second sweep
+    ssq = ssq_chunk<CH>(b, ssq);
+  }
+  const float norm = __fsqrt_rn(ssq);
+  const float inv = __fdiv_rn(1.0f, norm + 1e-8f);
+  if (valid) *norm_ptr = __half_as_ushort(__float2half_rn(norm));
+#pragma unroll 1
+  for (int c = 0; c < STEPS; c += 2) {
+    tmem_wait16(a); tmem_issue16(tacc + (c + 1) * CH, b);
+    quant_chunk_fast<BITS, CH>(a, inv, sc, idx_row + c * BYTES, valid);
+    tmem_wait16(b);
+    if (c + 2 < STEPS) tmem_issue16(tacc + (c + 2) * CH, a);
+    quant_chunk_fast<BITS, CH>(b, inv, sc, idx_row + (c + 1) * BYTES, valid);
   }
 }
 
@@ -389,6 +531,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
     const int wg_tid = (ew & 3) * 32 + lane;
     int cur_job = -1;
     bool ok = true;
+    bool fast = false;
+    Shortcut sc = {0.f, 0.f, 0.f, 0.f, 0.f};
     for (int i = wg; i < n_local && ok; i += 4) {
       const int t = t0 + i;
       const int j = find_job(batch, t, cur_job);
@@ -397,6 +541,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
         asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");     // previous tile's readers are done
         thr[wg_tid] = __ldg(job.codebook + kThresholdOff + wg_tid);
         thr[wg_tid + 128] = __ldg(job.codebook + kThresholdOff + 128 + wg_tid);
+        fast = __ldg(job.codebook + 512) != 0.f && job.bits <= 5;
+        sc.s = __ldg(job.codebook + 513);
+        sc.c1 = __ldg(job.codebook + 514);
+        sc.c2 = __ldg(job.codebook + 515);
+        sc.c3 = __ldg(job.codebook + 516);
+        sc.thr_lane = __ldg(job.codebook + kThresholdOff + lane);
         asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");
         cur_job = j;
       }
@@ -412,6 +562,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
       const int ipb = 8 / job.bits;
       uint8_t* idx_row = job.idx_out + n * (int64_t)(kDim / ipb);
       uint16_t* norm_ptr = job.norms_out + n;
+      if (fast) {
+        switch (job.bits) {
+          case 1: epilogue_tile_fast<1>(tacc, sc, idx_row, norm_ptr, valid); break;
+          case 2: epilogue_tile_fast<2>(tacc, sc, idx_row, norm_ptr, valid); break;
+          case 3: epilogue_tile_fast<3>(tacc, sc, idx_row, norm_ptr, valid); break;
+          case 4: epilogue_tile_fast<4>(tacc, sc, idx_row, norm_ptr, valid); break;
+          default: epilogue_tile_fast<5>(tacc, sc, idx_row, norm_ptr, valid); break;
+        }
+      } else
       switch (job.bits) {
         case 1: epilogue_tile<1>(tacc, thr, idx_row, norm_ptr, valid); break;
         case 2: epilogue_tile<2>(tacc, thr, idx_row, norm_ptr, valid); break;

@@ -17,7 +17,7 @@ LIB_PATH = os.path.join(_HERE, "libturboquant_b200.so")
 
 F32, F16, BF16 = 0, 1, 2
 IDX_PACKED, IDX_U8, IDX_I64 = 0, 1, 2
-CODEBOOK_FLOATS = 512
+CODEBOOK_FLOATS = 528
 SCORE_NOALLOC_SCRATCH_BYTES = 4 << 20
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
@@ -151,7 +151,7 @@ def packed_row_bytes(D: int, bits: int) -> int:
 
 
 def codebook_block(centroids: torch.Tensor, bits: int) -> torch.Tensor:
-    """512-float device-format block (centroids + exact decision thresholds), on the CPU."""
+    """Device-format codebook block (centroids, exact decision thresholds, search shortcut), on the CPU."""
     c = centroids.detach().to("cpu", torch.float32).contiguous()
     if c.numel() != 2 ** bits:
         raise ValueError(f"expected {2 ** bits} centroids, got {c.numel()}")
