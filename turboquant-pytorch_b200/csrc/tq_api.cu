@@ -92,10 +92,16 @@ void fit_shortcut(float* block, int n) {
     c[i] = acc / m[i][i];
   }
   const float c1 = (float)c[0], c2 = (float)c[1], c3 = (float)c[2];
+  // Kernels may fold the per-vector scale into s, which moves t by an ulp or two; demand the
+  // bracket for slightly perturbed scales as well so that such rounding can never matter.
+  const float s_lo = s * (1.0f - 4e-6f), s_hi = s * (1.0f + 4e-6f);
   auto ok_at = [&](float y) {
-    const int e = shortcut_e(y, s, c1, c2, c3);
     const int i = exact_index(y, thr, n);
-    return e >= 0 && e <= 31 && (e == i || e + 1 == i) && (e < n || i == e);
+    for (float sv : {s_lo, s, s_hi}) {
+      const int e = shortcut_e(y, sv, c1, c2, c3);
+      if (!(e >= 0 && e <= 31 && (e == i || e + 1 == i) && (e < n || i == e))) return false;
+    }
+    return true;
   };
   for (int k = 0; k < n; ++k) {
     float y = thr[k];

@@ -300,13 +300,14 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tmem_acc, const float* th
 // 2^23 bit patterns that ride along are removed once per word as a constant.
 struct Shortcut {
   float s, c1, c2, c3;
-  float thr_lane;      // threshold[lane] (+inf past the last one)
+  float thr_lane_h;    // threshold[lane] * 2^40 (+inf past the last one)
+  float s_inv, h_inv;  // per vector: s / (norm + 1e-8) and 2^40 / (norm + 1e-8)
 };
 
 // CH coordinates (16 here) per step: the loop body stays small enough to live in the
 // instruction cache while four warps per scheduler run it out of phase.
 template <int BITS, int CH>
-__device__ __forceinline__ void quant_chunk_fast(const uint32_t (&raw)[CH], float inv, const Shortcut& sc, uint8_t* dst,
+__device__ __forceinline__ void quant_chunk_fast(const uint32_t (&raw)[CH], const Shortcut& sc, uint8_t* dst,
                                                  bool valid) {
   constexpr int IPB = 8 / BITS;
   constexpr int BYTES = CH / IPB;               // packed bytes for CH coordinates
@@ -317,13 +318,19 @@ __device__ __forceinline__ void quant_chunk_fast(const uint32_t (&raw)[CH], floa
   for (int w = 0; w < WORDS; ++w) acc[w] = 0u;
 #pragma unroll
   for (int e = 0; e < CH; ++e) {
-    const float y = __uint_as_float(raw[e]) * inv;
-    const float t = __saturatef(fmaf(y, sc.s, 0.5f));
+    // t and the compare both come straight from the raw accumulator: y = raw * inv is never
+    // rounded on its own.  pf = sat((raw*inv - thr) * 2^40) is 1 when y > thr, 0 when y <= thr
+    // (a positive difference below 2^-40 cannot occur between an fp32 product and an fp32
+    // threshold unless they agree to ~1e-12, where either side is a valid answer).
+    const float r = __uint_as_float(raw[e]);
+    float t, pf;
+    asm("fma.rn.sat.f32 %0, %1, %2, 0f3F000000;" : "=f"(t) : "f"(r), "f"(sc.s_inv));
     float q = fmaf(sc.c3, t, sc.c2);
     q = fmaf(q, t, sc.c1);
     const float u = fmaf(q, t, 8388608.0f);
-    const float thr = __shfl_sync(0xffffffffu, sc.thr_lane, __float_as_int(u));
-    const float ui = u + ((y > thr) ? 1.0f : 0.0f);
+    const float thr_h = __shfl_sync(0xffffffffu, sc.thr_lane_h, __float_as_int(u));
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(pf) : "f"(r), "f"(sc.h_inv), "f"(-thr_h));
+    const float ui = u + pf;
     const int byte = e / IPB;
     const int shift = 8 * (byte & 3) + BITS * (IPB - 1 - (e % IPB));
     acc[byte >> 2] = __float_as_uint(ui) * (1u << shift) + acc[byte >> 2];
@@ -365,7 +372,7 @@ __device__ __forceinline__ float ssq_chunk(const uint32_t (&raw)[CH], float ssq)
 // Two register buffers alternate so that a TMEM load is always in flight behind the math;
 // the loops stay rolled (two inlined copies of the step body, one per buffer).
 template <int BITS>
-__device__ __forceinline__ void epilogue_tile_fast(uint32_t tacc, const Shortcut& sc, uint8_t* idx_row,
+__device__ __forceinline__ void epilogue_tile_fast(uint32_t tacc, Shortcut sc, uint8_t* idx_row,
                                                    uint16_t* norm_ptr, bool valid) {
   constexpr int CH = 16;
   constexpr int STEPS = kDim / CH;               // 8
@@ -382,14 +389,16 @@ __device__ __forceinline__ void epilogue_tile_fast(uint32_t tacc, const Shortcut
   }
   const float norm = __fsqrt_rn(ssq);
   const float inv = __fdiv_rn(1.0f, norm + 1e-8f);
+  sc.s_inv = sc.s * inv;
+  sc.h_inv = 1099511627776.0f * inv;          // 2^40: exact scaling
   if (valid) *norm_ptr = __half_as_ushort(__float2half_rn(norm));
 #pragma unroll 1
   for (int c = 0; c < STEPS; c += 2) {
     tmem_wait16(a); tmem_issue16(tacc + (c + 1) * CH, b);
-    quant_chunk_fast<BITS, CH>(a, inv, sc, idx_row + c * BYTES, valid);
+    quant_chunk_fast<BITS, CH>(a, sc, idx_row + c * BYTES, valid);
     tmem_wait16(b);
     if (c + 2 < STEPS) tmem_issue16(tacc + (c + 2) * CH, a);
-    quant_chunk_fast<BITS, CH>(b, inv, sc, idx_row + (c + 1) * BYTES, valid);
+    quant_chunk_fast<BITS, CH>(b, sc, idx_row + (c + 1) * BYTES, valid);
   }
 }
 
@@ -532,7 +541,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
     int cur_job = -1;
     bool ok = true;
     bool fast = false;
-    Shortcut sc = {0.f, 0.f, 0.f, 0.f, 0.f};
+    Shortcut sc = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int i = wg; i < n_local && ok; i += 4) {
       const int t = t0 + i;
       const int j = find_job(batch, t, cur_job);
@@ -546,7 +555,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
         sc.c1 = __ldg(job.codebook + 514);
         sc.c2 = __ldg(job.codebook + 515);
         sc.c3 = __ldg(job.codebook + 516);
-        sc.thr_lane = __ldg(job.codebook + kThresholdOff + lane);
+        sc.thr_lane_h = __ldg(job.codebook + kThresholdOff + lane) * 1099511627776.0f;
         asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");
         cur_job = j;
       }
