@@ -615,7 +615,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
 // x norm -> cache dtype -> 16-byte stores).  Warp 1 issues the MMAs, warp 0 brings in
 // the rotation image when the job changes.  16-bit outputs need one pass (c_hi . Pi_hi,
 // error ~3e-4 of a 2e-3 budget); fp32 output takes three (hi.hi + lo.hi + hi.lo ~ 2^-21).
-struct alignas(16) UmmaDeqJob {
+struct alignas(64) UmmaDeqJob {
+  CUtensorMap out_map;       // 16-bit outputs: (D, S, H, B) view of out, box 64 x 128, 128-byte swizzle
   const uint8_t* idx;
   const uint16_t* norms;
   const void* image;         // image of Pi^T
@@ -630,7 +631,7 @@ struct alignas(16) UmmaDeqJob {
   int32_t out_dtype;
   int32_t pad_;
 };
-constexpr int kMaxDeqJobs = 192;
+constexpr int kMaxDeqJobs = 96;
 struct UmmaDeqBatch {
   int32_t n_jobs;
   int32_t total_tiles;
@@ -639,16 +640,26 @@ struct UmmaDeqBatch {
 };
 static_assert(sizeof(UmmaDeqBatch) < 32000, "kernel parameter space");
 
+// Decoupled pipeline: producer (bulk copies of packed tiles) -> 8 expander warps (packed
+// bytes -> fp16 centroid pieces in the swizzled operand layout) -> MMA warp -> 8 drain warps
+// (TMEM -> x norm -> cache dtype -> 16-byte stores).  Each stage has its own ring, so global
+// load latency, expansion, tensor work and stores all overlap across tiles.
 template <bool OUT32>
 struct DCfg {
-  static constexpr int kWG = OUT32 ? 2 : 4;
+  static constexpr int kPk = OUT32 ? 2 : 3;                // packed-tile ring
+  static constexpr int kNA = 2;                            // operand ring
+  static constexpr int kNT = 4;                            // TMEM accumulators
   static constexpr int kPiecesA = OUT32 ? 2 : 1;
   static constexpr int kPiecesB = OUT32 ? 2 : 1;
-  static constexpr int kThreadsD = 64 + kWG * 128;
+  static constexpr int kExpWarps = 8, kDrainWarps = 8;
+  static constexpr int kThreadsD = 64 + 32 * (kExpWarps + kDrainWarps);     // 576
+  static constexpr uint32_t kPkBytes = 16384;              // 128 rows x up to 128 packed bytes
   static constexpr uint32_t kOffA = 0;
-  static constexpr uint32_t kOffPi = kOffA + kWG * kPiecesA * kTileBytes;
-  static constexpr uint32_t kOffLut = kOffPi + kPiecesB * kTileBytes;          // kWG x 256 words
-  static constexpr uint32_t kOffBar = kOffLut + kWG * 1024;
+  static constexpr uint32_t kOffPi = kOffA + kNA * kPiecesA * kTileBytes;
+  static constexpr uint32_t kOffPk = kOffPi + kPiecesB * kTileBytes;
+  static constexpr uint32_t kOffStage = kOffPk + kPk * kPkBytes;           // 16-bit outputs: one tile per drain group
+  static constexpr uint32_t kOffLut = kOffStage + (OUT32 ? 0u : 2u * kTileBytes);   // 256 words
+  static constexpr uint32_t kOffBar = kOffLut + 1024;
   static constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;
 };
 static_assert(DCfg<false>::kSmemBytes <= 232448 && DCfg<true>::kSmemBytes <= 232448, "shared memory budget");
@@ -662,44 +673,56 @@ __device__ __forceinline__ int find_djob(const UmmaDeqBatch& b, int tile, int fr
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 ld_shared_v2(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
 
-// Expand one row: G packed bytes -> 128 fp16 values per piece, 16-byte chunk q of k-half h
-// at  h*16384 + row*128 + ((q ^ (row & 7)) << 4).  lut[i] = {hi(c_i) | lo(c_i) << 16}.
+// Expand half a row (64 coordinates = one 128-byte swizzled operand row of k-half `half`):
+// chunk q (8 coordinates, 16 bytes) goes to  half*16384 + row*128 + ((q ^ (row & 7)) << 4).
+// lut[i] = {hi(c_i) | lo(c_i) << 16}; `src` is the shared address of this half row's bytes.
 template <int BITS, int PIECES>
-__device__ __forceinline__ void expand_row(const uint8_t* __restrict__ packed, const uint32_t* lut, uint32_t a_stage,
-                                           int row) {
+__device__ __forceinline__ void expand_half(uint32_t src, const uint32_t* lut, uint32_t a_stage, int row, int half) {
   constexpr int IPB = 8 / BITS;
-  constexpr int G = kDim / IPB;                 // bytes per row: 16, 32, 64, 128
+  constexpr int HB = kDim / IPB / 2;            // packed bytes per half row: 8, 16, 32, 64
   constexpr uint32_t MASK = (1u << BITS) - 1u;
-  const uint4* src = reinterpret_cast<const uint4*>(packed);
+  uint32_t w[HB / 4];
+  if constexpr (HB == 8) {
+    const uint2 v = ld_shared_v2(src);
+    w[0] = v.x; w[1] = v.y;
+  } else {
 #pragma unroll
-  for (int v = 0; v < G / 16; ++v) {
-    const uint4 raw = __ldg(src + v);
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-    constexpr int ELEMS = 16 * IPB;             // coordinates covered by these 16 bytes
-#pragma unroll
-    for (int q8 = 0; q8 < ELEMS / 8; ++q8) {    // one 16-byte operand chunk = 8 coordinates
-      uint32_t hi[4], lo[4];
-#pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        uint32_t e2[2];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int e = q8 * 8 + p * 2 + u;     // coordinate within this 16-byte load
-          const int byte = e / IPB;
-          const int sh = 8 * (byte & 3) + BITS * (IPB - 1 - (e % IPB));
-          e2[u] = lut[(w[byte >> 2] >> sh) & MASK];
-        }
-        hi[p] = __byte_perm(e2[0], e2[1], 0x5410);
-        lo[p] = __byte_perm(e2[0], e2[1], 0x7632);
-      }
-      const int coord = v * ELEMS + q8 * 8;     // first coordinate of the chunk, 0..127
-      const int half = coord >> 6;
-      const int q = (coord & 63) >> 3;
-      const uint32_t dst = a_stage + half * kHalfBytes + row * 128 + ((q ^ (row & 7)) << 4);
-      st_shared_v4(dst, hi[0], hi[1], hi[2], hi[3]);
-      if constexpr (PIECES == 2) st_shared_v4(dst + kTileBytes, lo[0], lo[1], lo[2], lo[3]);
+    for (int v = 0; v < HB / 16; ++v) {
+      const uint4 t = ld_shared_v4(src + 16 * v);
+      w[4 * v] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
     }
+  }
+  const uint32_t dst_row = a_stage + half * kHalfBytes + row * 128;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      uint32_t e2[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int e = q * 8 + p * 2 + u;        // coordinate within the half row
+        const int byte = e / IPB;
+        const int sh = 8 * (byte & 3) + BITS * (IPB - 1 - (e % IPB));
+        e2[u] = lut[(w[byte >> 2] >> sh) & MASK];
+      }
+      hi[p] = __byte_perm(e2[0], e2[1], 0x5410);
+      lo[p] = __byte_perm(e2[0], e2[1], 0x7632);
+    }
+    const uint32_t dst = dst_row + ((q ^ (row & 7)) << 4);
+    st_shared_v4(dst, hi[0], hi[1], hi[2], hi[3]);
+    if constexpr (PIECES == 2) st_shared_v4(dst + kTileBytes, lo[0], lo[1], lo[2], lo[3]);
   }
 }
 
@@ -707,50 +730,105 @@ __device__ __forceinline__ void expand_row(const uint8_t* __restrict__ packed, c
 // past the end of a slab included; `valid` only guards the stores.
 template <int ODT>
 __device__ __forceinline__ void drain_row(uint32_t tacc, float nv, void* out_row, bool valid) {
+  uint32_t a[16], b[16];
+  tmem_issue16(tacc, a);
 #pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
-    float v[32];
-    tmem_ld32(tacc + c * 32, v);
-    if (!valid) continue;
+  for (int c = 0; c < 8; c += 2) {
 #pragma unroll
-    for (int e = 0; e < 32; ++e) v[e] *= nv;
-    if constexpr (ODT == TQ_F32) {
-      float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(out_row) + c * 32);
+    for (int hb = 0; hb < 2; ++hb) {
+      uint32_t (&cur)[16] = hb ? b : a;
+      uint32_t (&nxt)[16] = hb ? a : b;
+      tmem_wait16(cur);
+      if (c + hb + 1 < 8) tmem_issue16(tacc + (c + hb + 1) * 16, nxt);
+      if (valid) {
+        float v[16];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) o[e] = make_float4(v[4 * e], v[4 * e + 1], v[4 * e + 2], v[4 * e + 3]);
-    } else {
-      uint32_t pk[16];
+        for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(cur[e]) * nv;
+        if constexpr (ODT == TQ_F32) {
+          float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(out_row) + (c + hb) * 16);
 #pragma unroll
-      for (int e = 0; e < 16; ++e) {
+          for (int e = 0; e < 4; ++e) o[e] = make_float4(v[4 * e], v[4 * e + 1], v[4 * e + 2], v[4 * e + 3]);
+        } else {
+          uint32_t pk[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            if constexpr (ODT == TQ_F16) {
+              __half2 h = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+              pk[e] = *reinterpret_cast<uint32_t*>(&h);
+            } else {
+              __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+              pk[e] = *reinterpret_cast<uint32_t*>(&h);
+            }
+          }
+          uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out_row) + (c + hb) * 16);
+          o[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          o[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        }
+      }
+    }
+  }
+}
+
+// 16-bit outputs: scale, convert and write the row into a staging tile laid out like an
+// operand tile (128-byte swizzle), from where one TMA store writes whole 128-byte lines to
+// global memory; rows past the end of a slab are clipped by the tensor map.
+template <int ODT>
+__device__ __forceinline__ void drain_row_staged(uint32_t tacc, float nv, uint32_t stage, int row) {
+  uint32_t a[16], b[16];
+  tmem_issue16(tacc, a);
+#pragma unroll 1
+  for (int c = 0; c < 8; c += 2) {
+#pragma unroll
+    for (int hb = 0; hb < 2; ++hb) {
+      uint32_t (&cur)[16] = hb ? b : a;
+      uint32_t (&nxt)[16] = hb ? a : b;
+      tmem_wait16(cur);
+      if (c + hb + 1 < 8) tmem_issue16(tacc + (c + hb + 1) * 16, nxt);
+      uint32_t pk[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float v0 = __uint_as_float(cur[2 * e]) * nv, v1 = __uint_as_float(cur[2 * e + 1]) * nv;
         if constexpr (ODT == TQ_F16) {
-          __half2 h = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+          __half2 h = __floats2half2_rn(v0, v1);
           pk[e] = *reinterpret_cast<uint32_t*>(&h);
         } else {
-          __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+          __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
           pk[e] = *reinterpret_cast<uint32_t*>(&h);
         }
       }
-      uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out_row) + c * 32);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) o[e] = make_uint4(pk[4 * e], pk[4 * e + 1], pk[4 * e + 2], pk[4 * e + 3]);
+      const int q0 = (c + hb) * 2;               // first 16-byte chunk of this step, 0..15
+      const uint32_t half_base = stage + (uint32_t)(q0 >> 3) * kHalfBytes + (uint32_t)row * 128u;
+      st_shared_v4(half_base + (uint32_t)((((q0 & 7)) ^ (row & 7)) << 4), pk[0], pk[1], pk[2], pk[3]);
+      st_shared_v4(half_base + (uint32_t)((((q0 & 7) + 1) ^ (row & 7)) << 4), pk[4], pk[5], pk[6], pk[7]);
     }
   }
+}
+
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
 }
 
 template <bool OUT32>
 __global__ void __launch_bounds__(DCfg<OUT32>::kThreadsD, 1) k_umma_dequantize(const __grid_constant__ UmmaDeqBatch batch) {
   using C = DCfg<OUT32>;
-  constexpr int kWG = C::kWG;
+  constexpr int kPk = C::kPk, kNA = C::kNA, kNT = C::kNT;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t a_smem = base + C::kOffA;
   const uint32_t pi_smem = base + C::kOffPi;
-  uint32_t* lut_all = reinterpret_cast<uint32_t*>(gbase + C::kOffLut);
+  const uint32_t pk_smem = base + C::kOffPk;
+  uint32_t* lut = reinterpret_cast<uint32_t*>(gbase + C::kOffLut);
   const uint32_t bar0 = base + C::kOffBar;
-  const uint32_t bar_full = bar0;                 // [kWG] A tile expanded
-  const uint32_t bar_tfull = bar0 + 8 * kWG;      // [kWG] accumulator ready
-  const uint32_t bar_pifull = bar_tfull + 8 * kWG;
+  const uint32_t bar_pkfull = bar0;                       // [kPk] producer -> expanders
+  const uint32_t bar_pkempty = bar_pkfull + 8 * kPk;      // [kPk] expanders (256 arrivals) -> producer
+  const uint32_t bar_afull = bar_pkempty + 8 * kPk;       // [kNA] expanders (256 arrivals) -> MMA
+  const uint32_t bar_aempty = bar_afull + 8 * kNA;        // [kNA] MMA commit -> expanders
+  const uint32_t bar_tfull = bar_aempty + 8 * kNA;        // [kNT] MMA commit -> drain
+  const uint32_t bar_tempty = bar_tfull + 8 * kNT;        // [kNT] drain (4 arrivals) -> MMA
+  const uint32_t bar_pifull = bar_tempty + 8 * kNT;
   const uint32_t bar_pifree = bar_pifull + 8;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + C::kOffBar + 200);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + C::kOffBar + 208);
@@ -762,7 +840,9 @@ __global__ void __launch_bounds__(DCfg<OUT32>::kThreadsD, 1) k_umma_dequantize(c
   const int n_local = t1 - t0;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kWG; ++i) { mbar_init(bar_full + 8 * i, 1); mbar_init(bar_tfull + 8 * i, 1); }
+    for (int i = 0; i < kPk; ++i) { mbar_init(bar_pkfull + 8 * i, 1); mbar_init(bar_pkempty + 8 * i, 256); }
+    for (int i = 0; i < kNA; ++i) { mbar_init(bar_afull + 8 * i, 256); mbar_init(bar_aempty + 8 * i, 1); }
+    for (int i = 0; i < kNT; ++i) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, 4); }
     mbar_init(bar_pifull, 1);
     mbar_init(bar_pifree, 1);
     *abort_flag = 0;
@@ -775,25 +855,44 @@ __global__ void __launch_bounds__(DCfg<OUT32>::kThreadsD, 1) k_umma_dequantize(c
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ---- rotation image loader
+    // ---- producer: rotation image on job change, packed tiles into the ring
     if (lane == 0) {
       int cur_job = -1, pi_loads = 0;
       bool ok = true;
       for (int i = 0; i < n_local && ok; ++i) {
-        const int j = find_djob(batch, t0 + i, cur_job);
-        if (j == cur_job) continue;
-        if (pi_loads > 0) ok = mbar_wait(bar_pifree, (uint32_t)((pi_loads - 1) & 1), abort_flag);
-        if (!ok) break;
-        mbar_arrive_expect_tx(bar_pifull, C::kPiecesB * kTileBytes);
-        const uint8_t* img = reinterpret_cast<const uint8_t*>(batch.jobs[j].image);
+        const int t = t0 + i;
+        const int j = find_djob(batch, t, cur_job);
+        const UmmaDeqJob& job = batch.jobs[j];
+        if (j != cur_job) {
+          if (pi_loads > 0) ok = mbar_wait(bar_pifree, (uint32_t)((pi_loads - 1) & 1), abort_flag);
+          if (!ok) break;
+          mbar_arrive_expect_tx(bar_pifull, C::kPiecesB * kTileBytes);
+          const uint8_t* img = reinterpret_cast<const uint8_t*>(job.image);
 #pragma unroll
-        for (int p = 0; p < C::kPiecesB; ++p) bulk_load(pi_smem + p * kTileBytes, img + p * kTileBytes, kTileBytes, bar_pifull);
-        ++pi_loads;
-        cur_job = j;
+          for (int p = 0; p < C::kPiecesB; ++p) bulk_load(pi_smem + p * kTileBytes, img + p * kTileBytes, kTileBytes, bar_pifull);
+          ++pi_loads;
+          cur_job = j;
+        }
+        const int s = i % kPk;
+        ok = mbar_wait(bar_pkempty + 8 * s, (uint32_t)(((i / kPk) & 1) ^ 1), abort_flag);
+        if (!ok) break;
+        const int lt = t - job.tile_begin;
+        const int slab = lt / job.tiles_per_slab;
+        const int64_t s0 = (int64_t)(lt - slab * job.tiles_per_slab) * kTileRows;
+        const int64_t rows = (job.S - s0) < kTileRows ? (job.S - s0) : kTileRows;
+        const int g = kDim / (8 / job.bits);
+        const uint32_t bytes = (uint32_t)(rows * g);
+        mbar_arrive_expect_tx(bar_pkfull + 8 * s, bytes);
+        bulk_load(pk_smem + s * C::kPkBytes, job.idx + ((int64_t)slab * job.S + s0) * g, bytes, bar_pkfull + 8 * s);
       }
       if (!ok) {
         *abort_flag = 1;
         if (batch.status != nullptr) atomicCAS(batch.status, 0, (4 << 16) | (int)blockIdx.x);
+      }
+      const int armed = n_local < kPk ? n_local : kPk;
+      for (int k = 0; k < armed; ++k) {
+        const int i = n_local - 1 - k;
+        if (i >= 0) mbar_wait(bar_pkfull + 8 * (i % kPk), (uint32_t)((i / kPk) & 1), abort_flag);
       }
       if (pi_loads > 0) mbar_wait(bar_pifull, (uint32_t)((pi_loads - 1) & 1), abort_flag);
     }
@@ -812,14 +911,15 @@ __global__ void __launch_bounds__(DCfg<OUT32>::kThreadsD, 1) k_umma_dequantize(c
           ++pi_uses;
           cur_job = j;
         }
-        const int g = i % kWG;
-        ok = mbar_wait(bar_full + 8 * g, (uint32_t)((i / kWG) & 1), abort_flag);
+        const int a = i % kNA, b = i % kNT;
+        ok = mbar_wait(bar_afull + 8 * a, (uint32_t)((i / kNA) & 1), abort_flag);
+        if (!ok) break;
+        ok = mbar_wait(bar_tempty + 8 * b, (uint32_t)(((i / kNT) & 1) ^ 1), abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(g * 128);
-        const uint32_t a_tile = a_smem + g * C::kPiecesA * kTileBytes;
-        // pass list: (A piece, B piece): hi.hi [, lo.hi, hi.lo]
-        constexpr int kPasses = OUT32 ? 3 : 1;
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * 128);
+        const uint32_t a_tile = a_smem + a * C::kPiecesA * kTileBytes;
+        constexpr int kPasses = OUT32 ? 3 : 1;      // hi.hi [, lo.hi, hi.lo]
 #pragma unroll
         for (int pass = 0; pass < kPasses; ++pass) {
           const int pa = (pass == 1) ? 1 : 0;
@@ -832,7 +932,8 @@ __global__ void __launch_bounds__(DCfg<OUT32>::kThreadsD, 1) k_umma_dequantize(c
             umma_f16(d_tmem, adesc, bdesc, idesc, (pass | k) != 0 ? 1u : 0u);
           }
         }
-        umma_commit(bar_tfull + 8 * g);
+        umma_commit(bar_aempty + 8 * a);
+        umma_commit(bar_tfull + 8 * b);
         const int next_job = (i + 1 < n_local) ? find_djob(batch, t + 1, cur_job) : -1;
         if (next_job != cur_job) umma_commit(bar_pifree);
       }
@@ -841,75 +942,114 @@ __global__ void __launch_bounds__(DCfg<OUT32>::kThreadsD, 1) k_umma_dequantize(c
         if (batch.status != nullptr) atomicCAS(batch.status, 0, (5 << 16) | (int)blockIdx.x);
       }
     }
-  } else {
-    // ---- warpgroups: expand, then drain
-    const int ew = warp - 2;
-    const int wg = ew >> 2;
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
-    uint32_t* lut = lut_all + wg * 256;
-    const int wg_tid = (ew & 3) * 32 + lane;
-    const uint32_t a_stage = a_smem + wg * C::kPiecesA * kTileBytes;
+  } else if (warp < 2 + C::kExpWarps) {
+    // ---- expanders: 256 threads, one half row each
+    const int et = threadIdx.x - 64;             // 0..255
+    const int row = et >> 1, half = et & 1;
     int cur_job = -1;
     bool ok = true;
-    for (int i = wg; i < n_local && ok; i += kWG) {
+    for (int i = 0; i < n_local && ok; ++i) {
       const int t = t0 + i;
       const int j = find_djob(batch, t, cur_job);
       const UmmaDeqJob& job = batch.jobs[j];
       if (j != cur_job) {
-        asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");
-        for (int e = wg_tid; e < 256; e += 128) {
-          const float c = __ldg(job.codebook + kCentroidOff + e);
-          const __half h = __float2half_rn(c);
-          const __half l = __float2half_rn(c - __half2float(h));
-          lut[e] = (uint32_t)__half_as_ushort(h) | ((uint32_t)__half_as_ushort(l) << 16);
-        }
-        asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");       // everyone is past the previous tile's look-ups
+        const float c = __ldg(job.codebook + kCentroidOff + et);
+        const __half h = __float2half_rn(c);
+        const __half l = __float2half_rn(c - __half2float(h));
+        lut[et] = (uint32_t)__half_as_ushort(h) | ((uint32_t)__half_as_ushort(l) << 16);
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         cur_job = j;
       }
+      const int s = i % kPk, a = i % kNA;
+      ok = mbar_wait(bar_pkfull + 8 * s, (uint32_t)((i / kPk) & 1), abort_flag);
+      if (!ok) break;
+      ok = mbar_wait(bar_aempty + 8 * a, (uint32_t)(((i / kNA) & 1) ^ 1), abort_flag);
+      if (!ok) break;
       const int lt = t - job.tile_begin;
       const int slab = lt / job.tiles_per_slab;
       const int64_t s_row = (int64_t)(lt - slab * job.tiles_per_slab) * kTileRows + row;
-      const bool valid = s_row < job.S;
-      const int64_t n = (int64_t)slab * job.S + s_row;
-      if (valid) {
-        const int ipb = 8 / job.bits;
-        const uint8_t* packed = job.idx + n * (int64_t)(kDim / ipb);
+      if (s_row < job.S) {
+        const int g = kDim / (8 / job.bits);
+        const uint32_t src = pk_smem + s * C::kPkBytes + (uint32_t)(row * g + half * (g >> 1));
+        const uint32_t a_stage = a_smem + a * C::kPiecesA * kTileBytes;
         switch (job.bits) {
-          case 1: expand_row<1, C::kPiecesA>(packed, lut, a_stage, row); break;
-          case 2: expand_row<2, C::kPiecesA>(packed, lut, a_stage, row); break;
-          case 3: expand_row<3, C::kPiecesA>(packed, lut, a_stage, row); break;
-          case 4: expand_row<4, C::kPiecesA>(packed, lut, a_stage, row); break;
-          case 5: expand_row<5, C::kPiecesA>(packed, lut, a_stage, row); break;
-          case 6: expand_row<6, C::kPiecesA>(packed, lut, a_stage, row); break;
-          case 7: expand_row<7, C::kPiecesA>(packed, lut, a_stage, row); break;
-          default: expand_row<8, C::kPiecesA>(packed, lut, a_stage, row); break;
+          case 1: expand_half<1, C::kPiecesA>(src, lut, a_stage, row, half); break;
+          case 2: expand_half<2, C::kPiecesA>(src, lut, a_stage, row, half); break;
+          case 3: expand_half<3, C::kPiecesA>(src, lut, a_stage, row, half); break;
+          case 4: expand_half<4, C::kPiecesA>(src, lut, a_stage, row, half); break;
+          case 5: expand_half<5, C::kPiecesA>(src, lut, a_stage, row, half); break;
+          case 6: expand_half<6, C::kPiecesA>(src, lut, a_stage, row, half); break;
+          case 7: expand_half<7, C::kPiecesA>(src, lut, a_stage, row, half); break;
+          default: expand_half<8, C::kPiecesA>(src, lut, a_stage, row, half); break;
         }
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      tc_fence_before();
-      asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");
-      if (wg_tid == 0) mbar_arrive(bar_full + 8 * wg);
-      ok = mbar_wait(bar_tfull + 8 * wg, (uint32_t)((i / kWG) & 1), abort_flag);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(wg * 128);
-      {
-        const float nv = valid ? __half2float(__ushort_as_half(job.norms[n])) : 0.f;
-        const int hh = slab % job.H, bb = slab / job.H;
-        const int64_t off = (int64_t)bb * job.os_b + (int64_t)hh * job.os_h + s_row * job.os_s;
-        if constexpr (OUT32) {
-          drain_row<TQ_F32>(tacc, nv, reinterpret_cast<float*>(job.out) + off, valid);
-        } else {
-          if (job.out_dtype == TQ_F16) drain_row<TQ_F16>(tacc, nv, reinterpret_cast<uint16_t*>(job.out) + off, valid);
-          else drain_row<TQ_BF16>(tacc, nv, reinterpret_cast<uint16_t*>(job.out) + off, valid);
-        }
-      }
-      tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // operand writes -> visible to the tensor core
+      mbar_arrive(bar_afull + 8 * a);
+      mbar_arrive(bar_pkempty + 8 * s);
     }
     if (!ok && lane == 0) {
       *abort_flag = 1;
       if (batch.status != nullptr) atomicCAS(batch.status, 0, (6 << 16) | (int)blockIdx.x);
+    }
+  } else {
+    // ---- drain: two warpgroups, alternate tiles
+    const int dw = warp - (2 + C::kExpWarps);    // 0..7
+    const int wg = dw >> 2;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int wg_tid = (dw & 3) * 32 + lane;
+    const uint32_t stage = base + C::kOffStage + (uint32_t)wg * kTileBytes;
+    int cur_job = -1;
+    bool ok = true;
+    for (int i = wg; i < n_local && ok; i += 2) {
+      const int t = t0 + i;
+      const int j = find_djob(batch, t, cur_job);
+      cur_job = j;
+      const UmmaDeqJob& job = batch.jobs[j];
+      const int lt = t - job.tile_begin;
+      const int slab = lt / job.tiles_per_slab;
+      const int s0 = (lt - slab * job.tiles_per_slab) * kTileRows;
+      const int64_t s_row = (int64_t)s0 + row;
+      const bool valid = s_row < job.S;
+      const int64_t n = (int64_t)slab * job.S + s_row;
+      const float nv = valid ? __half2float(__ushort_as_half(__ldg(job.norms + n))) : 0.f;   // in flight during the wait
+      const int hh = slab % job.H, bb = slab / job.H;
+      const int b = i % kNT;
+      ok = mbar_wait(bar_tfull + 8 * b, (uint32_t)((i / kNT) & 1), abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * 128);
+      if constexpr (OUT32) {
+        const int64_t off = (int64_t)bb * job.os_b + (int64_t)hh * job.os_h + s_row * job.os_s;
+        drain_row<TQ_F32>(tacc, nv, reinterpret_cast<float*>(job.out) + off, valid);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
+      } else {
+        // the previous tile's store must have finished reading the staging tile
+        if (wg_tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        asm volatile("bar.sync %0, 128;" ::"r"(wg + 2) : "memory");
+        if (job.out_dtype == TQ_F16) drain_row_staged<TQ_F16>(tacc, nv, stage, row);
+        else drain_row_staged<TQ_BF16>(tacc, nv, stage, row);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * b);               // the accumulator is free again
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staging writes -> visible to the TMA engine
+        asm volatile("bar.sync %0, 128;" ::"r"(wg + 2) : "memory");
+        if (wg_tid == 0) {
+          tma_store_4d(&job.out_map, stage, 0, s0, hh, bb);
+          tma_store_4d(&job.out_map, stage + kHalfBytes, 64, s0, hh, bb);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      }
+    }
+    if constexpr (!OUT32) {
+      if (wg_tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all stores done before exit
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      if (batch.status != nullptr) atomicCAS(batch.status, 0, (7 << 16) | (int)blockIdx.x);
     }
   }
   tc_fence_before();
@@ -1064,12 +1204,16 @@ bool umma_dequantize_eligible(const TqDequantizeJob& j) {
   if (((uintptr_t)j.idx & 15u) || ((uintptr_t)j.out & 15u) || ((uintptr_t)j.rotation_image & 15u)) return false;
   const int64_t q = j.out_dtype == TQ_F32 ? 4 : 8;     // elements per 16 bytes
   if (j.ostride_s % q != 0 || j.ostride_h % q != 0 || j.ostride_b % q != 0) return false;
+  if (j.ostride_s < 0 || j.ostride_h < 0 || j.ostride_b < 0) return false;
+  if (j.out_dtype != TQ_F32 && (j.B > 65535 || j.H > 65535 || (j.S > 1 && j.ostride_s < kDim))) return false;
   const int64_t tiles = j.B * j.H * ((j.S + kTileRows - 1) / kTileRows);
   return tiles < ((int64_t)1 << 30);
 }
 
 // One persistent launch over a run of eligible jobs that share the output class (fp32 vs 16-bit).
 int umma_dequantize(const TqDequantizeJob* jobs, int n_jobs, cudaStream_t st) {
+  EncodeTiledFn enc = encode_fn();
+  if (enc == nullptr) return TQ_ELAUNCH;
   static thread_local UmmaDeqBatch batch;
   int done = 0;
   while (done < n_jobs) {
@@ -1079,6 +1223,19 @@ int umma_dequantize(const TqDequantizeJob* jobs, int n_jobs, cudaStream_t st) {
       const TqDequantizeJob& j = jobs[done + i];
       UmmaDeqJob& u = batch.jobs[i];
       const int64_t tps = (j.S + kTileRows - 1) / kTileRows;
+      if (j.out_dtype != TQ_F32) {
+        const int64_t ss = j.S > 1 ? j.ostride_s : kDim;
+        const int64_t sh = j.H > 1 ? j.ostride_h : ss * j.S;
+        const int64_t sb = j.B > 1 ? j.ostride_b : (sh > ss ? sh : ss) * (j.H > 1 ? j.H : j.S);
+        cuuint64_t dims[4] = {(cuuint64_t)kDim, (cuuint64_t)j.S, (cuuint64_t)j.H, (cuuint64_t)j.B};
+        cuuint64_t strides[3] = {(cuuint64_t)ss * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
+        cuuint32_t box[4] = {64, (cuuint32_t)kTileRows, 1, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        CUresult r = enc(&u.out_map, j.out_dtype == TQ_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                         4, j.out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { note_cuda_error(100000 + (int)r); return TQ_ELAUNCH; }
+      }
       u.idx = reinterpret_cast<const uint8_t*>(j.idx);
       u.norms = j.norms;
       u.image = j.rotation_image;
