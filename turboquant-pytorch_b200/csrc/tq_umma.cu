@@ -945,7 +945,7 @@ __global__ void __launch_bounds__(DCfg<OUT32>::kThreadsD, 1) k_umma_dequantize(c
   } else if (warp < 2 + C::kExpWarps) {
     // ---- expanders: 256 threads, one half row each
     const int et = threadIdx.x - 64;             // 0..255
-    const int row = et >> 1, half = et & 1;
+    const int row = et & 127, half = et >> 7;   // a quarter warp = 8 rows of one k-half: conflict-free operand stores
     int cur_job = -1;
     bool ok = true;
     for (int i = 0; i < n_local && ok; ++i) {
