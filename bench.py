@@ -80,7 +80,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            time.sleep(0.02)
+            time.sleep(0.0005)
 
     def __enter__(self):
         if self._nv is not None:
