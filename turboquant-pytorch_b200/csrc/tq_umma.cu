@@ -40,7 +40,6 @@ constexpr uint32_t kTileBytes = kTileRows * kDim * 2;  // 32768
 constexpr uint32_t kHalfBytes = kTileBytes / 2;        // one 64-column box
 constexpr uint32_t kImageBytes = 5 * kTileBytes;       // fp16 hi, lo; then bf16 p0, p1, p2
 constexpr int kMaxJobs = 96;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // every mbarrier wait gives up after 2 s
 
 // shared memory map (offsets from a 1024-byte aligned base)
 template <bool BF16>
@@ -75,6 +74,8 @@ struct UmmaQuantBatch {
   int32_t n_jobs;
   int32_t total_tiles;
   int32_t* status;           // device status word (may be null)
+  int32_t ablate;            // timing experiments only (TQ_ABLATE): 1 skip stores, 2 skip index math, 4 skip MMA
+  int32_t pad_[3];
   UmmaQuantJob jobs[kMaxJobs];
 };
 
@@ -105,20 +106,19 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: false when the time limit ran out or another role aborted.
+// Bounded wait: false when the limit ran out (about two seconds of SM clocks) or another
+// role aborted.  The clock is only consulted every 256 polls: reading a timer on every miss
+// would put its latency on every hand-off of the pipeline.
+constexpr long long kWaitLimitCycles = 4000000000ll;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long start = global_ns();
+  long long start = 0;
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 0u) {
+    if ((it & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (global_ns() - start > kWaitLimitNs) return false;
+      const long long now = clock64();
+      if (start == 0) start = now;
+      else if (now - start > kWaitLimitCycles) return false;
     }
   }
 }
@@ -129,6 +129,14 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global [%0, {%1, %2, %3, %4}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2),
+               "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
@@ -232,21 +240,47 @@ __device__ __forceinline__ uint32_t idesc_f16(bool bf16) {
   return (1u << 4) | (fmt << 7) | (fmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 }
 
-// job that owns `tile`; tiles only grow within a role, so the scan resumes from `from`
-__device__ __forceinline__ int find_job(const UmmaQuantBatch& b, int tile, int from) {
-  int j = from < 0 ? 0 : from;
+// Register copy of the job a role is working on.  The table lives in kernel-parameter space,
+// where every field access with a run-time index is a slow dependent load; a role therefore
+// reloads the fields only when its tile leaves the current job's range.
+struct QuantJobView {
+  int j = -1, begin = 0, end = 0;      // tiles [begin, end)
+  int tps = 1, H = 1, bits = 0, g = 0; // tiles per slab, heads, code width, packed bytes per row
+  int64_t S = 0;
+  uint8_t* idx_out = nullptr;
+  uint16_t* norms_out = nullptr;
+  const float* codebook = nullptr;
+  const void* image = nullptr;
+  const CUtensorMap* tmap = nullptr;
+};
+// true when `tile` belongs to another job than the cached one (tiles only grow within a role)
+__device__ __forceinline__ bool view_advance(const UmmaQuantBatch& b, int tile, QuantJobView& v) {
+  if (v.j >= 0 && tile < v.end) return false;
+  int j = v.j < 0 ? 0 : v.j;
   while (j + 1 < b.n_jobs && tile >= b.jobs[j + 1].tile_begin) ++j;
-  return j;
+  const UmmaQuantJob& job = b.jobs[j];
+  v.j = j;
+  v.begin = job.tile_begin;
+  v.end = (j + 1 < b.n_jobs) ? b.jobs[j + 1].tile_begin : b.total_tiles;
+  v.tps = job.tiles_per_slab;
+  v.H = job.H;
+  v.bits = job.bits;
+  v.g = kDim / (8 / job.bits);
+  v.S = job.S;
+  v.idx_out = job.idx_out;
+  v.norms_out = job.norms_out;
+  v.codebook = job.codebook;
+  v.image = job.image;
+  v.tmap = &job.tmap;
+  return true;
 }
 
 // ---------------------------------------------------------------- epilogue
 // One thread owns one vector.  BITS is a compile-time constant so that the
 // search and the packing unroll completely.
-template <int BITS>
-__device__ __forceinline__ void epilogue_tile(uint32_t tmem_acc, const float* thr, uint8_t* idx_row, uint16_t* norm_ptr,
-                                              bool valid) {
-  constexpr int IPB = 8 / BITS;
-  constexpr int BYTES_PER_CHUNK = 32 / IPB;     // packed bytes per 32 coordinates
+// Generic (binary search) epilogue for code widths without a search shortcut.  A thread
+// owns all 128 coordinates of one vector; tmem_acc points at its first column.
+__device__ __forceinline__ float ssq_row_generic(uint32_t tmem_acc) {
   float ssq = 0.f;
 #pragma unroll 1
   for (int c = 0; c < 4; ++c) {
@@ -255,9 +289,14 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tmem_acc, const float* th
 #pragma unroll
     for (int e = 0; e < 32; ++e) ssq = fmaf(v[e], v[e], ssq);
   }
-  const float norm = __fsqrt_rn(ssq);
-  const float inv = __fdiv_rn(1.0f, norm + 1e-8f);
-  if (valid) *norm_ptr = __half_as_ushort(__float2half_rn(norm));
+  return ssq;
+}
+
+template <int BITS>
+__device__ __forceinline__ void quant_row_generic(uint32_t tmem_acc, float inv, const float* thr, uint8_t* idx_half,
+                                                  bool valid) {
+  constexpr int IPB = 8 / BITS;
+  constexpr int BYTES_PER_CHUNK = 32 / IPB;     // packed bytes per 32 coordinates
 #pragma unroll 1
   for (int c = 0; c < 4; ++c) {
     float v[32];
@@ -281,14 +320,14 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tmem_acc, const float* th
     }
     if (valid) {
       if constexpr (BYTES_PER_CHUNK == 4) {
-        *reinterpret_cast<uint32_t*>(idx_row + c * 4) = words[0];
+        *reinterpret_cast<uint32_t*>(idx_half + c * 4) = words[0];
       } else if constexpr (BYTES_PER_CHUNK == 8) {
-        *reinterpret_cast<uint2*>(idx_row + c * 8) = make_uint2(words[0], words[1]);
+        *reinterpret_cast<uint2*>(idx_half + c * 8) = make_uint2(words[0], words[1]);
       } else if constexpr (BYTES_PER_CHUNK == 16) {
-        *reinterpret_cast<uint4*>(idx_row + c * 16) = make_uint4(words[0], words[1], words[2], words[3]);
+        *reinterpret_cast<uint4*>(idx_half + c * 16) = make_uint4(words[0], words[1], words[2], words[3]);
       } else {
-        *reinterpret_cast<uint4*>(idx_row + c * 32) = make_uint4(words[0], words[1], words[2], words[3]);
-        *reinterpret_cast<uint4*>(idx_row + c * 32 + 16) = make_uint4(words[4], words[5], words[6], words[7]);
+        *reinterpret_cast<uint4*>(idx_half + c * 32) = make_uint4(words[0], words[1], words[2], words[3]);
+        *reinterpret_cast<uint4*>(idx_half + c * 32 + 16) = make_uint4(words[4], words[5], words[6], words[7]);
       }
     }
   }
@@ -306,7 +345,7 @@ struct Shortcut {
 
 // CH coordinates (16 here) per step: the loop body stays small enough to live in the
 // instruction cache while four warps per scheduler run it out of phase.
-template <int BITS, int CH>
+template <int BITS, int CH, bool NOSHFL = false>
 __device__ __forceinline__ void quant_chunk_fast(const uint32_t (&raw)[CH], const Shortcut& sc, uint8_t* dst,
                                                  bool valid) {
   constexpr int IPB = 8 / BITS;
@@ -328,7 +367,7 @@ __device__ __forceinline__ void quant_chunk_fast(const uint32_t (&raw)[CH], cons
     float q = fmaf(sc.c3, t, sc.c2);
     q = fmaf(q, t, sc.c1);
     const float u = fmaf(q, t, 8388608.0f);
-    const float thr_h = __shfl_sync(0xffffffffu, sc.thr_lane_h, __float_as_int(u));
+    const float thr_h = NOSHFL ? sc.thr_lane_h : __shfl_sync(0xffffffffu, sc.thr_lane_h, __float_as_int(u));
     asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(pf) : "f"(r), "f"(sc.h_inv), "f"(-thr_h));
     const float ui = u + pf;
     const int byte = e / IPB;
@@ -369,36 +408,33 @@ __device__ __forceinline__ float ssq_chunk(const uint32_t (&raw)[CH], float ssq)
   return ssq;
 }
 
-// Two register buffers alternate so that a TMEM load is always in flight behind the math;
-// the loops stay rolled (two inlined copies of the step body, one per buffer).
-template <int BITS>
-__device__ __forceinline__ void epilogue_tile_fast(uint32_t tacc, Shortcut sc, uint8_t* idx_row,
-                                                   uint16_t* norm_ptr, bool valid) {
-  constexpr int CH = 16;
-  constexpr int STEPS = kDim / CH;               // 8
-  constexpr int BYTES = CH / (8 / BITS);
-  uint32_t a[CH], b[CH];
+// A thread owns one vector: eight 16-column steps per sweep.  Two register buffers
+// alternate so that a TMEM load is always in flight behind the math; the loops stay rolled
+// (two inlined copies of the step body, one per buffer).
+__device__ __forceinline__ float ssq_row_fast(uint32_t tacc, uint32_t (&a)[16], uint32_t (&b)[16]) {
   float ssq = 0.f;
   tmem_issue16(tacc, a);
 #pragma unroll 1
-  for (int c = 0; c < STEPS; c += 2) {
-    tmem_wait16(a); tmem_issue16(tacc + (c + 1) * CH, b);
-    ssq = ssq_chunk<CH>(a, ssq);
-    tmem_wait16(b); tmem_issue16(tacc + ((c + 2) & (STEPS - 1)) * CH, a);   // wraps to step 0 for the second sweep
-    ssq = ssq_chunk<CH>(b, ssq);
+  for (int c = 0; c < 8; c += 2) {
+    tmem_wait16(a); tmem_issue16(tacc + (c + 1) * 16, b);
+    ssq = ssq_chunk<16>(a, ssq);
+    tmem_wait16(b); tmem_issue16(tacc + ((c + 2) & 7) * 16, a);      // wraps to step 0 for the second sweep
+    ssq = ssq_chunk<16>(b, ssq);
   }
-  const float norm = __fsqrt_rn(ssq);
-  const float inv = __fdiv_rn(1.0f, norm + 1e-8f);
-  sc.s_inv = sc.s * inv;
-  sc.h_inv = 1099511627776.0f * inv;          // 2^40: exact scaling
-  if (valid) *norm_ptr = __half_as_ushort(__float2half_rn(norm));
+  return ssq;       // step 0 is in flight into `a`
+}
+
+template <int BITS, bool NOSHFL = false>
+__device__ __forceinline__ void quant_row_fast(uint32_t tacc, uint32_t (&a)[16], uint32_t (&b)[16], const Shortcut& sc,
+                                               uint8_t* idx_row, bool valid) {
+  constexpr int BYTES = 16 / (8 / BITS);
 #pragma unroll 1
-  for (int c = 0; c < STEPS; c += 2) {
-    tmem_wait16(a); tmem_issue16(tacc + (c + 1) * CH, b);
-    quant_chunk_fast<BITS, CH>(a, sc, idx_row + c * BYTES, valid);
+  for (int c = 0; c < 8; c += 2) {
+    tmem_wait16(a); tmem_issue16(tacc + (c + 1) * 16, b);
+    quant_chunk_fast<BITS, 16, NOSHFL>(a, sc, idx_row + c * BYTES, valid);
     tmem_wait16(b);
-    if (c + 2 < STEPS) tmem_issue16(tacc + (c + 2) * CH, a);
-    quant_chunk_fast<BITS, CH>(b, sc, idx_row + (c + 1) * BYTES, valid);
+    if (c + 2 < 8) tmem_issue16(tacc + (c + 2) * 16, a);
+    quant_chunk_fast<BITS, 16, NOSHFL>(b, sc, idx_row + (c + 1) * BYTES, valid);
   }
 }
 
@@ -448,13 +484,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int cur_job = -1, pi_loads = 0;
+      int pi_loads = 0;
       bool ok = true;
+      QuantJobView job;
       for (int i = 0; i < n_local && ok; ++i) {
         const int t = t0 + i;
-        const int j = find_job(batch, t, cur_job);
-        const UmmaQuantJob& job = batch.jobs[j];
-        if (j != cur_job) {
+        if (view_advance(batch, t, job)) {
           if (pi_loads > 0) ok = mbar_wait(bar_pifree, (uint32_t)((pi_loads - 1) & 1), abort_flag);
           if (!ok) break;
           mbar_arrive_expect_tx(bar_pifull, kPieces * kTileBytes);
@@ -462,18 +497,27 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
 #pragma unroll
           for (int p = 0; p < kPieces; ++p) bulk_load(pi_smem + p * kTileBytes, img + p * kTileBytes, kTileBytes, bar_pifull);
           ++pi_loads;
-          cur_job = j;
         }
         const int s = i % kStages;
-        ok = mbar_wait(bar_empty + 8 * s, (uint32_t)(((i / kStages) & 1) ^ 1), abort_flag);
-        if (!ok) break;
-        const int lt = t - job.tile_begin;
-        const int slab = lt / job.tiles_per_slab;
-        const int row0 = (lt - slab * job.tiles_per_slab) * kTileRows;
-        const int hh = slab % job.H, bb = slab / job.H;
-        mbar_arrive_expect_tx(bar_full + 8 * s, kTileBytes);
-        tma_load_4d(a_smem + s * kTileBytes, &job.tmap, 0, row0, hh, bb, bar_full + 8 * s);
-        tma_load_4d(a_smem + s * kTileBytes + kHalfBytes, &job.tmap, 64, row0, hh, bb, bar_full + 8 * s);
+        if (i >= kStages) {     // the stage is free once the MMAs of tile i - kStages are done (one commit serves both rings)
+          const int d = i - kStages;
+          ok = mbar_wait(bar_tfull + 8 * (d % kAccBufs), (uint32_t)((d / kAccBufs) & 1), abort_flag);
+          if (!ok) break;
+        }
+        const int lt = t - job.begin;
+        const int slab = lt / job.tps;
+        const int row0 = (lt - slab * job.tps) * kTileRows;
+        const int bb = slab / job.H, hh = slab - bb * job.H;
+        if (batch.ablate & 64) {
+          mbar_arrive(bar_full + 8 * s);
+        } else if (batch.ablate & 32) {
+          mbar_arrive_expect_tx(bar_full + 8 * s, kHalfBytes);
+          tma_load_4d(a_smem + s * kTileBytes, job.tmap, 0, row0, hh, bb, bar_full + 8 * s);
+        } else {
+          mbar_arrive_expect_tx(bar_full + 8 * s, kTileBytes);
+          tma_load_4d(a_smem + s * kTileBytes, job.tmap, 0, row0, hh, bb, bar_full + 8 * s);
+          tma_load_4d(a_smem + s * kTileBytes + kHalfBytes, job.tmap, 64, row0, hh, bb, bar_full + 8 * s);
+        }
       }
       if (!ok) {
         *abort_flag = 1;
@@ -490,16 +534,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      int cur_job = -1, pi_uses = 0;
+      int pi_uses = 0;
       bool ok = true;
+      QuantJobView job;
       for (int i = 0; i < n_local && ok; ++i) {
         const int t = t0 + i;
-        const int j = find_job(batch, t, cur_job);
-        if (j != cur_job) {
+        if (view_advance(batch, t, job)) {
           ok = mbar_wait(bar_pifull, (uint32_t)(pi_uses & 1), abort_flag);
           if (!ok) break;
           ++pi_uses;
-          cur_job = j;
         }
         const int s = i % kStages, b = i % kAccBufs;
         ok = mbar_wait(bar_full + 8 * s, (uint32_t)((i / kStages) & 1), abort_flag);
@@ -507,23 +550,28 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
         ok = mbar_wait(bar_tempty + 8 * b, (uint32_t)(((i / kAccBufs) & 1) ^ 1), abort_flag);
         if (!ok) break;
         tc_fence_after();
+        // One thread issues all MMAs, so the issue loop must stay a handful of instructions per
+        // MMA or the tensor pipe starves: descriptors are a per-tile base plus compile-time
+        // offsets (the start-address field counts 16-byte units and cannot carry out).
         const uint32_t idesc = idesc_f16(BF16);
         const uint32_t d_tmem = tmem_base + (uint32_t)(b * 128);
-        const uint32_t a_tile = a_smem + s * kTileBytes;
+        const uint64_t a_base = smem_desc_sw128(a_smem + s * kTileBytes);
+        const uint64_t b_base = smem_desc_sw128(pi_smem);
+        if (!(batch.ablate & 4)) {
 #pragma unroll
-        for (int piece = 0; piece < kPieces; ++piece) {
+          for (int piece = 0; piece < kPieces; ++piece) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const uint32_t koff = (uint32_t)((k >> 2) * kHalfBytes + (k & 3) * 32);
-            const uint64_t adesc = smem_desc_sw128(a_tile + koff);
-            const uint64_t bdesc = smem_desc_sw128(pi_smem + piece * kTileBytes + koff);
-            umma_f16(d_tmem, adesc, bdesc, idesc, (piece | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < 8; ++k) {
+              constexpr uint32_t kUnit = 16;
+              const uint64_t koff = (uint64_t)(((k >> 2) * kHalfBytes + (k & 3) * 32) / kUnit);
+              const uint64_t poff = (uint64_t)((piece * kTileBytes) / kUnit);
+              umma_f16(d_tmem, a_base + koff, b_base + poff + koff, idesc, (piece | k) != 0 ? 1u : 0u);
+            }
           }
         }
-        umma_commit(bar_empty + 8 * s);
-        umma_commit(bar_tfull + 8 * b);
-        const int next_job = (i + 1 < n_local) ? find_job(batch, t + 1, cur_job) : -1;
-        if (next_job != cur_job) umma_commit(bar_pifree);
+        if (batch.ablate & 128) mbar_arrive(bar_tfull + 8 * b); else
+        umma_commit(bar_tfull + 8 * b);      // one commit per tile: the epilogue and the producer both wait on it
+        if (i + 1 >= n_local || t + 1 >= job.end) umma_commit(bar_pifree);    // last tile of this job here
       }
       if (!ok) {
         *abort_flag = 1;
@@ -538,15 +586,13 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
     const int row = quarter * 32 + lane;
     float* thr = thr_all + wg * 256;
     const int wg_tid = (ew & 3) * 32 + lane;
-    int cur_job = -1;
     bool ok = true;
     bool fast = false;
     Shortcut sc = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    QuantJobView job;
     for (int i = wg; i < n_local && ok; i += 4) {
       const int t = t0 + i;
-      const int j = find_job(batch, t, cur_job);
-      const UmmaQuantJob& job = batch.jobs[j];
-      if (j != cur_job) {
+      if (view_advance(batch, t, job)) {
         asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");     // previous tile's readers are done
         thr[wg_tid] = __ldg(job.codebook + kThresholdOff + wg_tid);
         thr[wg_tid + 128] = __ldg(job.codebook + kThresholdOff + 128 + wg_tid);
@@ -557,38 +603,49 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
         sc.c3 = __ldg(job.codebook + 516);
         sc.thr_lane_h = __ldg(job.codebook + kThresholdOff + lane) * 1099511627776.0f;
         asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");
-        cur_job = j;
       }
       ok = mbar_wait(bar_tfull + 8 * wg, (uint32_t)((i / kAccBufs) & 1), abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const int lt = t - job.tile_begin;
-      const int slab = lt / job.tiles_per_slab;
-      const int64_t s_row = (int64_t)(lt - slab * job.tiles_per_slab) * kTileRows + row;
-      const bool valid = s_row < job.S;
+      const int lt = t - job.begin;
+      const int slab = lt / job.tps;
+      const int64_t s_row = (int64_t)(lt - slab * job.tps) * kTileRows + row;
+      const bool valid = s_row < job.S && !(batch.ablate & 1);
       const int64_t n = (int64_t)slab * job.S + s_row;
       const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(wg * 128);
-      const int ipb = 8 / job.bits;
-      uint8_t* idx_row = job.idx_out + n * (int64_t)(kDim / ipb);
-      uint16_t* norm_ptr = job.norms_out + n;
-      if (fast) {
-        switch (job.bits) {
-          case 1: epilogue_tile_fast<1>(tacc, sc, idx_row, norm_ptr, valid); break;
-          case 2: epilogue_tile_fast<2>(tacc, sc, idx_row, norm_ptr, valid); break;
-          case 3: epilogue_tile_fast<3>(tacc, sc, idx_row, norm_ptr, valid); break;
-          case 4: epilogue_tile_fast<4>(tacc, sc, idx_row, norm_ptr, valid); break;
-          default: epilogue_tile_fast<5>(tacc, sc, idx_row, norm_ptr, valid); break;
+      uint8_t* idx_row = job.idx_out + n * (int64_t)job.g;
+      if (!(batch.ablate & 2)) {
+        uint32_t ra[16], rb[16];
+        const float ssq = fast ? ssq_row_fast(tacc, ra, rb) : ssq_row_generic(tacc);
+        const float norm = __fsqrt_rn(ssq);
+        const float inv = __fdiv_rn(1.0f, norm + 1e-8f);
+        if (valid) job.norms_out[n] = __half_as_ushort(__float2half_rn(norm));
+        if (fast) {
+          sc.s_inv = sc.s * inv;
+          sc.h_inv = 1099511627776.0f * inv;          // 2^40: exact scaling
+          if (batch.ablate & 16) {
+            if (job.bits == 4) quant_row_fast<4, true>(tacc, ra, rb, sc, idx_row, valid);
+            else quant_row_fast<2, true>(tacc, ra, rb, sc, idx_row, valid);
+          } else
+          switch (job.bits) {
+            case 1: quant_row_fast<1>(tacc, ra, rb, sc, idx_row, valid); break;
+            case 2: quant_row_fast<2>(tacc, ra, rb, sc, idx_row, valid); break;
+            case 3: quant_row_fast<3>(tacc, ra, rb, sc, idx_row, valid); break;
+            case 4: quant_row_fast<4>(tacc, ra, rb, sc, idx_row, valid); break;
+            default: quant_row_fast<5>(tacc, ra, rb, sc, idx_row, valid); break;
+          }
+        } else {
+          switch (job.bits) {
+            case 1: quant_row_generic<1>(tacc, inv, thr, idx_row, valid); break;
+            case 2: quant_row_generic<2>(tacc, inv, thr, idx_row, valid); break;
+            case 3: quant_row_generic<3>(tacc, inv, thr, idx_row, valid); break;
+            case 4: quant_row_generic<4>(tacc, inv, thr, idx_row, valid); break;
+            case 5: quant_row_generic<5>(tacc, inv, thr, idx_row, valid); break;
+            case 6: quant_row_generic<6>(tacc, inv, thr, idx_row, valid); break;
+            case 7: quant_row_generic<7>(tacc, inv, thr, idx_row, valid); break;
+            default: quant_row_generic<8>(tacc, inv, thr, idx_row, valid); break;
+          }
         }
-      } else
-      switch (job.bits) {
-        case 1: epilogue_tile<1>(tacc, thr, idx_row, norm_ptr, valid); break;
-        case 2: epilogue_tile<2>(tacc, thr, idx_row, norm_ptr, valid); break;
-        case 3: epilogue_tile<3>(tacc, thr, idx_row, norm_ptr, valid); break;
-        case 4: epilogue_tile<4>(tacc, thr, idx_row, norm_ptr, valid); break;
-        case 5: epilogue_tile<5>(tacc, thr, idx_row, norm_ptr, valid); break;
-        case 6: epilogue_tile<6>(tacc, thr, idx_row, norm_ptr, valid); break;
-        case 7: epilogue_tile<7>(tacc, thr, idx_row, norm_ptr, valid); break;
-        default: epilogue_tile<8>(tacc, thr, idx_row, norm_ptr, valid); break;
       }
       tc_fence_before();
       __syncwarp();
@@ -636,6 +693,8 @@ struct UmmaDeqBatch {
   int32_t n_jobs;
   int32_t total_tiles;
   int32_t* status;
+  int32_t ablate;            // timing experiments only (TQ_ABLATE): 1 skip stores, 2 skip expansion, 4 skip MMA
+  int32_t pad_[3];
   UmmaDeqJob jobs[kMaxDeqJobs];
 };
 static_assert(sizeof(UmmaDeqBatch) < 32000, "kernel parameter space");
@@ -644,25 +703,29 @@ static_assert(sizeof(UmmaDeqBatch) < 32000, "kernel parameter space");
 // bytes -> fp16 centroid pieces in the swizzled operand layout) -> MMA warp -> 8 drain warps
 // (TMEM -> x norm -> cache dtype -> 16-byte stores).  Each stage has its own ring, so global
 // load latency, expansion, tensor work and stores all overlap across tiles.
-template <bool OUT32>
+// NARROW: every job of the launch has codes of at most 4 bits, so a packed tile is at most
+// 8 KB; the space saved buys a deeper packed ring and a third operand stage.
+template <bool OUT32, bool NARROW>
 struct DCfg {
-  static constexpr int kPk = OUT32 ? 2 : 3;                // packed-tile ring
-  static constexpr int kNA = 2;                            // operand ring
+  static constexpr int kPk = NARROW ? 4 : (OUT32 ? 2 : 3); // packed-tile ring
+  static constexpr int kNA = (NARROW && !OUT32) ? 3 : 2;   // operand ring
   static constexpr int kNT = 4;                            // TMEM accumulators
   static constexpr int kPiecesA = OUT32 ? 2 : 1;
   static constexpr int kPiecesB = OUT32 ? 2 : 1;
   static constexpr int kExpWarps = 8, kDrainWarps = 8;
   static constexpr int kThreadsD = 64 + 32 * (kExpWarps + kDrainWarps);     // 576
-  static constexpr uint32_t kPkBytes = 16384;              // 128 rows x up to 128 packed bytes
+  static constexpr uint32_t kPkBytes = NARROW ? 8192 : 16384;   // 128 rows x up to 64 / 128 packed bytes
   static constexpr uint32_t kOffA = 0;
   static constexpr uint32_t kOffPi = kOffA + kNA * kPiecesA * kTileBytes;
   static constexpr uint32_t kOffPk = kOffPi + kPiecesB * kTileBytes;
   static constexpr uint32_t kOffStage = kOffPk + kPk * kPkBytes;           // 16-bit outputs: one tile per drain group
-  static constexpr uint32_t kOffLut = kOffStage + (OUT32 ? 0u : 2u * kTileBytes);   // 256 words
-  static constexpr uint32_t kOffBar = kOffLut + 1024;
+  static constexpr uint32_t kOffBar = kOffStage + (OUT32 ? 0u : 2u * kTileBytes);
   static constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;
 };
-static_assert(DCfg<false>::kSmemBytes <= 232448 && DCfg<true>::kSmemBytes <= 232448, "shared memory budget");
+// + 1 KB of static shared memory for the centroid look-up table
+static_assert(DCfg<false, false>::kSmemBytes + 1024 <= 232448 && DCfg<true, false>::kSmemBytes + 1024 <= 232448 &&
+              DCfg<false, true>::kSmemBytes + 1024 <= 232448 && DCfg<true, true>::kSmemBytes + 1024 <= 232448,
+              "shared memory budget");
 
 __device__ __forceinline__ int find_djob(const UmmaDeqBatch& b, int tile, int from) {
   int j = from < 0 ? 0 : from;
@@ -686,7 +749,15 @@ __device__ __forceinline__ uint2 ld_shared_v2(uint32_t addr) {
 
 // Expand half a row (64 coordinates = one 128-byte swizzled operand row of k-half `half`):
 // chunk q (8 coordinates, 16 bytes) goes to  half*16384 + row*128 + ((q ^ (row & 7)) << 4).
-// lut[i] = {hi(c_i) | lo(c_i) << 16}; `src` is the shared address of this half row's bytes.
+// lut[i] = {hi(c_i) | lo(c_i) << 16} in static shared memory; `src` is the shared address
+// of this half row's packed bytes.  Look-ups use byte offsets (index * 4) so that the load
+// is a plain [register + constant] shared-memory access; for 4- and 2-bit codes the offsets
+// of a whole word are prepared with two shifts and masks and picked out bytewise.
+template <int BITS>
+__device__ __forceinline__ uint32_t lut_at(const uint32_t* lut, uint32_t byte_off) {
+  return *reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(lut) + byte_off);
+}
+
 template <int BITS, int PIECES>
 __device__ __forceinline__ void expand_half(uint32_t src, const uint32_t* lut, uint32_t a_stage, int row, int half) {
   constexpr int IPB = 8 / BITS;
@@ -706,19 +777,43 @@ __device__ __forceinline__ void expand_half(uint32_t src, const uint32_t* lut, u
   const uint32_t dst_row = a_stage + half * kHalfBytes + row * 128;
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
+    uint32_t e2[8];                             // look-ups of the 8 coordinates of this chunk
+    if constexpr (BITS == 4) {
+      const uint32_t x = w[q];                  // one word = 8 coordinates, two per byte
+      const uint32_t even = (x >> 2) & 0x3C3C3C3Cu, odd = (x << 2) & 0x3C3C3C3Cu;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        e2[2 * k] = lut_at<BITS>(lut, __byte_perm(even, 0u, 0x4440u | k));
+        e2[2 * k + 1] = lut_at<BITS>(lut, __byte_perm(odd, 0u, 0x4440u | k));
+      }
+    } else if constexpr (BITS == 2) {
+      const uint32_t x = w[q >> 1];             // one word = 16 coordinates, four per byte
+      const uint32_t f0 = (x >> 4) & 0x0C0C0C0Cu, f1 = (x >> 2) & 0x0C0C0C0Cu, f2 = x & 0x0C0C0C0Cu,
+                     f3 = (x << 2) & 0x0C0C0C0Cu;
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const uint32_t sel = 0x4440u | ((q & 1) * 2 + k);
+        e2[4 * k] = lut_at<BITS>(lut, __byte_perm(f0, 0u, sel));
+        e2[4 * k + 1] = lut_at<BITS>(lut, __byte_perm(f1, 0u, sel));
+        e2[4 * k + 2] = lut_at<BITS>(lut, __byte_perm(f2, 0u, sel));
+        e2[4 * k + 3] = lut_at<BITS>(lut, __byte_perm(f3, 0u, sel));
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int e = q * 8 + u;                // coordinate within the half row
+        const int byte = e / IPB;
+        const int sh = 8 * (byte & 3) + BITS * (IPB - 1 - (e % IPB));
+        const uint32_t xw = w[byte >> 2];
+        const uint32_t off = sh >= 2 ? ((xw >> (sh - 2)) & (MASK << 2)) : ((xw << (2 - sh)) & (MASK << 2));
+        e2[u] = lut_at<BITS>(lut, off);
+      }
+    }
     uint32_t hi[4], lo[4];
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
-      uint32_t e2[2];
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int e = q * 8 + p * 2 + u;        // coordinate within the half row
-        const int byte = e / IPB;
-        const int sh = 8 * (byte & 3) + BITS * (IPB - 1 - (e % IPB));
-        e2[u] = lut[(w[byte >> 2] >> sh) & MASK];
-      }
-      hi[p] = __byte_perm(e2[0], e2[1], 0x5410);
-      lo[p] = __byte_perm(e2[0], e2[1], 0x7632);
+      hi[p] = __byte_perm(e2[2 * p], e2[2 * p + 1], 0x5410);
+      lo[p] = __byte_perm(e2[2 * p], e2[2 * p + 1], 0x7632);
     }
     const uint32_t dst = dst_row + ((q ^ (row & 7)) << 4);
     st_shared_v4(dst, hi[0], hi[1], hi[2], hi[3]);
@@ -810,9 +905,9 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t sr
                : "memory");
 }
 
-template <bool OUT32>
-__global__ void __launch_bounds__(DCfg<OUT32>::kThreadsD, 1) k_umma_dequantize(const __grid_constant__ UmmaDeqBatch batch) {
-  using C = DCfg<OUT32>;
+template <bool OUT32, bool NARROW>
+__global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequantize(const __grid_constant__ UmmaDeqBatch batch) {
+  using C = DCfg<OUT32, NARROW>;
   constexpr int kPk = C::kPk, kNA = C::kNA, kNT = C::kNT;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -820,7 +915,7 @@ __global__ void __launch_bounds__(DCfg<OUT32>::kThreadsD, 1) k_umma_dequantize(c
   const uint32_t a_smem = base + C::kOffA;
   const uint32_t pi_smem = base + C::kOffPi;
   const uint32_t pk_smem = base + C::kOffPk;
-  uint32_t* lut = reinterpret_cast<uint32_t*>(gbase + C::kOffLut);
+  __shared__ uint32_t lut[256];                           // static: look-ups compile to [register + constant]
   const uint32_t bar0 = base + C::kOffBar;
   const uint32_t bar_pkfull = bar0;                       // [kPk] producer -> expanders
   const uint32_t bar_pkempty = bar_pkfull + 8 * kPk;      // [kPk] expanders (256 arrivals) -> producer
@@ -918,22 +1013,23 @@ __global__ void __launch_bounds__(DCfg<OUT32>::kThreadsD, 1) k_umma_dequantize(c
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(b * 128);
-        const uint32_t a_tile = a_smem + a * C::kPiecesA * kTileBytes;
+        const uint64_t a_base = smem_desc_sw128(a_smem + a * C::kPiecesA * kTileBytes);
+        const uint64_t b_base = smem_desc_sw128(pi_smem);
         constexpr int kPasses = OUT32 ? 3 : 1;      // hi.hi [, lo.hi, hi.lo]
+        if (!(batch.ablate & 4)) {
 #pragma unroll
-        for (int pass = 0; pass < kPasses; ++pass) {
-          const int pa = (pass == 1) ? 1 : 0;
-          const int pb = (pass == 2) ? 1 : 0;
+          for (int pass = 0; pass < kPasses; ++pass) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const uint32_t koff = (uint32_t)((k >> 2) * kHalfBytes + (k & 3) * 32);
-            const uint64_t adesc = smem_desc_sw128(a_tile + pa * kTileBytes + koff);
-            const uint64_t bdesc = smem_desc_sw128(pi_smem + pb * kTileBytes + koff);
-            umma_f16(d_tmem, adesc, bdesc, idesc, (pass | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < 8; ++k) {
+              // descriptor = per-tile base + compile-time offset in 16-byte units
+              const uint64_t koff = (uint64_t)(((k >> 2) * kHalfBytes + (k & 3) * 32) / 16);
+              const uint64_t pa = (uint64_t)(((pass == 1) ? kTileBytes : 0u) / 16);
+              const uint64_t pb = (uint64_t)(((pass == 2) ? kTileBytes : 0u) / 16);
+              umma_f16(d_tmem, a_base + pa + koff, b_base + pb + koff, idesc, (pass | k) != 0 ? 1u : 0u);
+            }
           }
         }
-        umma_commit(bar_aempty + 8 * a);
-        umma_commit(bar_tfull + 8 * b);
+        umma_commit(bar_tfull + 8 * b);      // one commit per tile: drain and expanders both wait on it
         const int next_job = (i + 1 < n_local) ? find_djob(batch, t + 1, cur_job) : -1;
         if (next_job != cur_job) umma_commit(bar_pifree);
       }
@@ -964,12 +1060,15 @@ __global__ void __launch_bounds__(DCfg<OUT32>::kThreadsD, 1) k_umma_dequantize(c
       const int s = i % kPk, a = i % kNA;
       ok = mbar_wait(bar_pkfull + 8 * s, (uint32_t)((i / kPk) & 1), abort_flag);
       if (!ok) break;
-      ok = mbar_wait(bar_aempty + 8 * a, (uint32_t)(((i / kNA) & 1) ^ 1), abort_flag);
-      if (!ok) break;
+      if (i >= kNA) {           // the operand stage is free once the MMAs of tile i - kNA are done
+        const int d = i - kNA;
+        ok = mbar_wait(bar_tfull + 8 * (d % kNT), (uint32_t)((d / kNT) & 1), abort_flag);
+        if (!ok) break;
+      }
       const int lt = t - job.tile_begin;
       const int slab = lt / job.tiles_per_slab;
       const int64_t s_row = (int64_t)(lt - slab * job.tiles_per_slab) * kTileRows + row;
-      if (s_row < job.S) {
+      if (s_row < job.S && !(batch.ablate & 2)) {
         const int g = kDim / (8 / job.bits);
         const uint32_t src = pk_smem + s * C::kPkBytes + (uint32_t)(row * g + half * (g >> 1));
         const uint32_t a_stage = a_smem + a * C::kPiecesA * kTileBytes;
@@ -1030,14 +1129,15 @@ __global__ void __launch_bounds__(DCfg<OUT32>::kThreadsD, 1) k_umma_dequantize(c
         // the previous tile's store must have finished reading the staging tile
         if (wg_tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         asm volatile("bar.sync %0, 128;" ::"r"(wg + 2) : "memory");
-        if (job.out_dtype == TQ_F16) drain_row_staged<TQ_F16>(tacc, nv, stage, row);
+        if (batch.ablate & 8) {
+        } else if (job.out_dtype == TQ_F16) drain_row_staged<TQ_F16>(tacc, nv, stage, row);
         else drain_row_staged<TQ_BF16>(tacc, nv, stage, row);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_tempty + 8 * b);               // the accumulator is free again
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staging writes -> visible to the TMA engine
         asm volatile("bar.sync %0, 128;" ::"r"(wg + 2) : "memory");
-        if (wg_tid == 0) {
+        if (wg_tid == 0 && !(batch.ablate & 1)) {
           tma_store_4d(&job.out_map, stage, 0, s0, hh, bb);
           tma_store_4d(&job.out_map, stage + kHalfBytes, 64, s0, hh, bb);
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -1103,6 +1203,11 @@ EncodeTiledFn encode_fn() {
     p = fn;
   }
   return reinterpret_cast<EncodeTiledFn>(p);
+}
+
+int ablate_flags() {
+  const char* e = getenv("TQ_ABLATE");
+  return e != nullptr ? atoi(e) : 0;
 }
 
 bool force_simt() {
@@ -1176,6 +1281,7 @@ int umma_quantize(const TqQuantizeJob* jobs, int n_jobs, cudaStream_t st) {
     }
     batch.n_jobs = take;
     batch.total_tiles = (int32_t)tile_cursor;
+    batch.ablate = ablate_flags();
     void* status_ptr = nullptr;
     cudaGetSymbolAddress(&status_ptr, g_umma_status);
     batch.status = reinterpret_cast<int32_t*>(status_ptr);
@@ -1254,6 +1360,7 @@ int umma_dequantize(const TqDequantizeJob* jobs, int n_jobs, cudaStream_t st) {
     }
     batch.n_jobs = take;
     batch.total_tiles = (int32_t)tile_cursor;
+    batch.ablate = ablate_flags();
     void* status_ptr = nullptr;
     cudaGetSymbolAddress(&status_ptr, g_umma_status);
     batch.status = reinterpret_cast<int32_t*>(status_ptr);
@@ -1262,16 +1369,20 @@ int umma_dequantize(const TqDequantizeJob* jobs, int n_jobs, cudaStream_t st) {
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = (int)(tile_cursor < sms ? tile_cursor : sms);
     const bool out32 = jobs[done].out_dtype == TQ_F32;
-    cudaError_t e;
-    if (out32) {
-      e = cudaFuncSetAttribute(k_umma_dequantize<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DCfg<true>::kSmemBytes);
+    bool narrow = true;
+    for (int i = 0; i < take; ++i) narrow = narrow && jobs[done + i].bits <= 4;
+    auto launch = [&](auto kern, uint32_t smem, int threads) -> int {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) { note_cuda_error((int)e); return TQ_ELAUNCH; }
-      k_umma_dequantize<true><<<grid, DCfg<true>::kThreadsD, DCfg<true>::kSmemBytes, st>>>(batch);
-    } else {
-      e = cudaFuncSetAttribute(k_umma_dequantize<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DCfg<false>::kSmemBytes);
-      if (e != cudaSuccess) { note_cuda_error((int)e); return TQ_ELAUNCH; }
-      k_umma_dequantize<false><<<grid, DCfg<false>::kThreadsD, DCfg<false>::kSmemBytes, st>>>(batch);
-    }
+      kern<<<grid, threads, smem, st>>>(batch);
+      return TQ_OK;
+    };
+    int lrc;
+    if (out32 && narrow) lrc = launch(k_umma_dequantize<true, true>, DCfg<true, true>::kSmemBytes, DCfg<true, true>::kThreadsD);
+    else if (out32) lrc = launch(k_umma_dequantize<true, false>, DCfg<true, false>::kSmemBytes, DCfg<true, false>::kThreadsD);
+    else if (narrow) lrc = launch(k_umma_dequantize<false, true>, DCfg<false, true>::kSmemBytes, DCfg<false, true>::kThreadsD);
+    else lrc = launch(k_umma_dequantize<false, false>, DCfg<false, false>::kSmemBytes, DCfg<false, false>::kThreadsD);
+    if (lrc != TQ_OK) return lrc;
     int rc = check_launch();
     if (rc != TQ_OK) return rc;
     done += take;
