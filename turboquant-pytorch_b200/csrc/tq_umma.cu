@@ -727,10 +727,39 @@ static_assert(DCfg<false, false>::kSmemBytes + 1024 <= 232448 && DCfg<true, fals
               DCfg<false, true>::kSmemBytes + 1024 <= 232448 && DCfg<true, true>::kSmemBytes + 1024 <= 232448,
               "shared memory budget");
 
-__device__ __forceinline__ int find_djob(const UmmaDeqBatch& b, int tile, int from) {
-  int j = from < 0 ? 0 : from;
+// Register copy of the current job (see QuantJobView).
+struct DeqJobView {
+  int j = -1, begin = 0, end = 0;
+  int tps = 1, H = 1, bits = 0, g = 0, out_dtype = 0;
+  int64_t S = 0, os_b = 0, os_h = 0, os_s = 0;
+  const uint8_t* idx = nullptr;
+  const uint16_t* norms = nullptr;
+  const float* codebook = nullptr;
+  const void* image = nullptr;
+  void* out = nullptr;
+  const CUtensorMap* out_map = nullptr;
+};
+__device__ __forceinline__ bool view_advance(const UmmaDeqBatch& b, int tile, DeqJobView& v) {
+  if (v.j >= 0 && tile < v.end) return false;
+  int j = v.j < 0 ? 0 : v.j;
   while (j + 1 < b.n_jobs && tile >= b.jobs[j + 1].tile_begin) ++j;
-  return j;
+  const UmmaDeqJob& job = b.jobs[j];
+  v.j = j;
+  v.begin = job.tile_begin;
+  v.end = (j + 1 < b.n_jobs) ? b.jobs[j + 1].tile_begin : b.total_tiles;
+  v.tps = job.tiles_per_slab;
+  v.H = job.H;
+  v.bits = job.bits;
+  v.g = kDim / (8 / job.bits);
+  v.out_dtype = job.out_dtype;
+  v.S = job.S; v.os_b = job.os_b; v.os_h = job.os_h; v.os_s = job.os_s;
+  v.idx = job.idx;
+  v.norms = job.norms;
+  v.codebook = job.codebook;
+  v.image = job.image;
+  v.out = job.out;
+  v.out_map = &job.out_map;
+  return true;
 }
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -952,13 +981,12 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
   if (warp == 0) {
     // ---- producer: rotation image on job change, packed tiles into the ring
     if (lane == 0) {
-      int cur_job = -1, pi_loads = 0;
+      int pi_loads = 0;
       bool ok = true;
+      DeqJobView job;
       for (int i = 0; i < n_local && ok; ++i) {
         const int t = t0 + i;
-        const int j = find_djob(batch, t, cur_job);
-        const UmmaDeqJob& job = batch.jobs[j];
-        if (j != cur_job) {
+        if (view_advance(batch, t, job)) {
           if (pi_loads > 0) ok = mbar_wait(bar_pifree, (uint32_t)((pi_loads - 1) & 1), abort_flag);
           if (!ok) break;
           mbar_arrive_expect_tx(bar_pifull, C::kPiecesB * kTileBytes);
@@ -966,16 +994,15 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
 #pragma unroll
           for (int p = 0; p < C::kPiecesB; ++p) bulk_load(pi_smem + p * kTileBytes, img + p * kTileBytes, kTileBytes, bar_pifull);
           ++pi_loads;
-          cur_job = j;
         }
         const int s = i % kPk;
         ok = mbar_wait(bar_pkempty + 8 * s, (uint32_t)(((i / kPk) & 1) ^ 1), abort_flag);
         if (!ok) break;
-        const int lt = t - job.tile_begin;
-        const int slab = lt / job.tiles_per_slab;
-        const int64_t s0 = (int64_t)(lt - slab * job.tiles_per_slab) * kTileRows;
+        const int lt = t - job.begin;
+        const int slab = lt / job.tps;
+        const int64_t s0 = (int64_t)(lt - slab * job.tps) * kTileRows;
         const int64_t rows = (job.S - s0) < kTileRows ? (job.S - s0) : kTileRows;
-        const int g = kDim / (8 / job.bits);
+        const int g = job.g;
         const uint32_t bytes = (uint32_t)(rows * g);
         mbar_arrive_expect_tx(bar_pkfull + 8 * s, bytes);
         bulk_load(pk_smem + s * C::kPkBytes, job.idx + ((int64_t)slab * job.S + s0) * g, bytes, bar_pkfull + 8 * s);
@@ -994,17 +1021,16 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
   } else if (warp == 1) {
     // ---- MMA issuer
     if (lane == 0) {
-      int cur_job = -1, pi_uses = 0;
+      int pi_uses = 0;
       bool ok = true;
       const uint32_t idesc = idesc_f16(false);
+      DeqJobView job;
       for (int i = 0; i < n_local && ok; ++i) {
         const int t = t0 + i;
-        const int j = find_djob(batch, t, cur_job);
-        if (j != cur_job) {
+        if (view_advance(batch, t, job)) {
           ok = mbar_wait(bar_pifull, (uint32_t)(pi_uses & 1), abort_flag);
           if (!ok) break;
           ++pi_uses;
-          cur_job = j;
         }
         const int a = i % kNA, b = i % kNT;
         ok = mbar_wait(bar_afull + 8 * a, (uint32_t)((i / kNA) & 1), abort_flag);
@@ -1030,8 +1056,7 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
           }
         }
         umma_commit(bar_tfull + 8 * b);      // one commit per tile: drain and expanders both wait on it
-        const int next_job = (i + 1 < n_local) ? find_djob(batch, t + 1, cur_job) : -1;
-        if (next_job != cur_job) umma_commit(bar_pifree);
+        if (i + 1 >= n_local || t + 1 >= job.end) umma_commit(bar_pifree);    // last tile of this job here
       }
       if (!ok) {
         *abort_flag = 1;
@@ -1042,20 +1067,17 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
     // ---- expanders: 256 threads, one half row each
     const int et = threadIdx.x - 64;             // 0..255
     const int row = et & 127, half = et >> 7;   // a quarter warp = 8 rows of one k-half: conflict-free operand stores
-    int cur_job = -1;
     bool ok = true;
+    DeqJobView job;
     for (int i = 0; i < n_local && ok; ++i) {
       const int t = t0 + i;
-      const int j = find_djob(batch, t, cur_job);
-      const UmmaDeqJob& job = batch.jobs[j];
-      if (j != cur_job) {
+      if (view_advance(batch, t, job)) {
         asm volatile("bar.sync 1, 256;" ::: "memory");       // everyone is past the previous tile's look-ups
         const float c = __ldg(job.codebook + kCentroidOff + et);
         const __half h = __float2half_rn(c);
         const __half l = __float2half_rn(c - __half2float(h));
         lut[et] = (uint32_t)__half_as_ushort(h) | ((uint32_t)__half_as_ushort(l) << 16);
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        cur_job = j;
       }
       const int s = i % kPk, a = i % kNA;
       ok = mbar_wait(bar_pkfull + 8 * s, (uint32_t)((i / kPk) & 1), abort_flag);
@@ -1065,11 +1087,11 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
         ok = mbar_wait(bar_tfull + 8 * (d % kNT), (uint32_t)((d / kNT) & 1), abort_flag);
         if (!ok) break;
       }
-      const int lt = t - job.tile_begin;
-      const int slab = lt / job.tiles_per_slab;
-      const int64_t s_row = (int64_t)(lt - slab * job.tiles_per_slab) * kTileRows + row;
+      const int lt = t - job.begin;
+      const int slab = lt / job.tps;
+      const int64_t s_row = (int64_t)(lt - slab * job.tps) * kTileRows + row;
       if (s_row < job.S && !(batch.ablate & 2)) {
-        const int g = kDim / (8 / job.bits);
+        const int g = job.g;
         const uint32_t src = pk_smem + s * C::kPkBytes + (uint32_t)(row * g + half * (g >> 1));
         const uint32_t a_stage = a_smem + a * C::kPiecesA * kTileBytes;
         switch (job.bits) {
@@ -1099,21 +1121,19 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
     const int row = quarter * 32 + lane;
     const int wg_tid = (dw & 3) * 32 + lane;
     const uint32_t stage = base + C::kOffStage + (uint32_t)wg * kTileBytes;
-    int cur_job = -1;
     bool ok = true;
+    DeqJobView job;
     for (int i = wg; i < n_local && ok; i += 2) {
       const int t = t0 + i;
-      const int j = find_djob(batch, t, cur_job);
-      cur_job = j;
-      const UmmaDeqJob& job = batch.jobs[j];
-      const int lt = t - job.tile_begin;
-      const int slab = lt / job.tiles_per_slab;
-      const int s0 = (lt - slab * job.tiles_per_slab) * kTileRows;
+      view_advance(batch, t, job);
+      const int lt = t - job.begin;
+      const int slab = lt / job.tps;
+      const int s0 = (lt - slab * job.tps) * kTileRows;
       const int64_t s_row = (int64_t)s0 + row;
       const bool valid = s_row < job.S;
       const int64_t n = (int64_t)slab * job.S + s_row;
       const float nv = valid ? __half2float(__ushort_as_half(__ldg(job.norms + n))) : 0.f;   // in flight during the wait
-      const int hh = slab % job.H, bb = slab / job.H;
+      const int bb = slab / job.H, hh = slab - bb * job.H;
       const int b = i % kNT;
       ok = mbar_wait(bar_tfull + 8 * b, (uint32_t)((i / kNT) & 1), abort_flag);
       if (!ok) break;
@@ -1138,8 +1158,8 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staging writes -> visible to the TMA engine
         asm volatile("bar.sync %0, 128;" ::"r"(wg + 2) : "memory");
         if (wg_tid == 0 && !(batch.ablate & 1)) {
-          tma_store_4d(&job.out_map, stage, 0, s0, hh, bb);
-          tma_store_4d(&job.out_map, stage + kHalfBytes, 64, s0, hh, bb);
+          tma_store_4d(job.out_map, stage, 0, s0, hh, bb);
+          tma_store_4d(job.out_map, stage + kHalfBytes, 64, s0, hh, bb);
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
       }
