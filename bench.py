@@ -35,6 +35,11 @@ WORKLOAD = ("configs[1]: Qwen2.5-3B-shaped KV cache, 36 layers x 2 KV heads x se
             "N(0,1) with 4/128 outlier channels x10, TurboQuantV3 K4/V2, residual_window=0, protected_layers=0")
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per full 72-job launch, from the ncu captures summarised in
+# profiles/ (18 layers captured, doubled: traffic grows in proportion to the vectors processed)
+NCU_DRAM_BYTES_PER_LAUNCH = {"quantize": 338.0e6, "dequantize": 244.4e6}
+
+
 def algorithmic_bytes_per_vector(bits: int, elem_bytes: int = 2) -> int:
     """D*sizeof(elem) + packed row + fp16 norm, for quantise and for dequantise to the cache dtype."""
     ipb = 8 // bits
@@ -279,7 +284,10 @@ def main():
                          "inputs and outputs (302 MB each) exceed the 126 MB L2",
                    "timing": "CUDA events around the quantize phase and the dequantize phase of every step, summed; max over ranks"},
         "roofline": {"bound": "hbm", "kernel": dominant[0], "achieved": dominant[1], "peak": peak_gbs, "unit": "GB/s",
-                     "frac": dominant[1] / peak_gbs, "traffic": None, "peak_source": peak_src,
+                     "frac": dominant[1] / peak_gbs, "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(dominant[0]) if
+                     (n_layers == LAYERS and kb == KEY_BITS and vb == VALUE_BITS) else None,
+                     "traffic_source": "ncu dram__bytes_read+write of an 18-layer capture x2 (profiles/)",
+                     "peak_source": peak_src,
                      "phases": {"quantize": {"GB/s": ach_q, "frac": ach_q / peak_gbs, "ms": 1e3 * t_q / args.steps,
                                              "algorithmic_bytes": bytes_q},
                                 "dequantize": {"GB/s": ach_d, "frac": ach_d / peak_gbs, "ms": 1e3 * t_d / args.steps,
