@@ -148,6 +148,115 @@ def run_reference(args, rank: int):
     }))
 
 
+def _time_steps(fn, steps, warmup, flush):
+    """CUDA-event time of `steps` calls of fn (seconds), L2 flushed before each, flush outside the intervals."""
+    for _ in range(warmup):
+        fn()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    torch.cuda.synchronize()
+    for a, b in evs:
+        flush.zero_()
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    return sum(a.elapsed_time(b) for a, b in evs) * 1e-3
+
+
+def run_side_workload(args, dev):
+    """Other rows of the path, measured with the same hygiene; one JSON line each.
+
+    scores: configs[3] (decode logits + softmax straight from 4-bit packed keys, 32 query heads on 8 KV heads,
+            131072 keys per head, one launch set per layer instance);
+    qjl:    configs[4] (V2 MSE+QJL compress, then asymmetric scores for 64 queries per head, head_dim 256);
+    llama:  configs[2] shape per layer ((8, 8, 32768, 128) bf16, K6/V4, window 128, protected layers at 8 bits),
+            `--layers` layers of it (two protected, the rest not).
+    """
+    import turboquant as tq
+    from turboquant import batched
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    out = {"n_gpus": 1, "steps": steps, "warmup": warmup, "higher_is_better": True, "data": "synthetic"}
+    if args.workload == "scores":
+        inst = args.layers if args.layers != LAYERS else 32
+        sk, hkv, hq = 131072, 8, 32
+        comps, packed, qs = [], [], []
+        for l in range(inst):
+            comp = tq.MSECompressor(HEAD_DIM, 4, seed=42 + 1000 * l, device=dev)
+            g = torch.Generator(device=dev).manual_seed(40000 + l)
+            keys = torch.randn(1, hkv, sk, HEAD_DIM, generator=g, device=dev, dtype=torch.float32)
+            keys[:, :, :, :4] *= 10.0
+            packed.append(comp.compress(keys.half()))
+            qs.append(torch.randn(1, hq, 1, HEAD_DIM, generator=g, device=dev))
+            comps.append(comp)
+            del keys
+        def step():
+            for c, p, q in zip(comps, packed, qs):
+                c.attention_scores(q, p, softmax=True)
+        t = _time_steps(step, steps, warmup, flush)
+        keys_n = inst * hkv * sk
+        by = keys_n * (64 + 2 + 2 * 4 * (hq // hkv))
+        out.update(metric="cached keys/s scored from packed 4-bit keys (logits + softmax)", unit="keys/s",
+                   value=keys_n * steps / t, ms_per_step=1e3 * t / steps, dtype="f32",
+                   config={"workload": f"configs[3]: {inst} layer instances x 8 KV heads x 131072 4-bit keys, 32 query heads"},
+                   roofline={"bound": "hbm", "achieved": by * steps / t / 1e9, "peak": peak, "unit": "GB/s",
+                             "frac": by * steps / t / 1e9 / peak, "traffic": None})
+    elif args.workload == "qjl":
+        comp = tq.TurboQuantCompressorV2(256, 3, seed=7, device=dev)
+        g = torch.Generator(device=dev).manual_seed(50000)
+        x = torch.randn(1, 16, 16384, 256, generator=g, device=dev).half()
+        q = torch.randn(1, 16, 64, 256, generator=g, device=dev)
+        c = comp.compress(x)
+        t1 = _time_steps(lambda: comp.compress(x), steps, warmup, flush)
+        t2 = _time_steps(lambda: comp.asymmetric_attention_scores(q, c), steps, warmup, flush)
+        n = 16 * 16384
+        out.update(metric="V2 MSE+QJL: vectors/s compress, keys/s scored (64 queries)", unit="vectors/s",
+                   value=n * steps / t1, ms_per_step=1e3 * t1 / steps, dtype="f32",
+                   config={"workload": "configs[4]: (1,16,16384,256) fp16, 3-bit TurboQuantCompressorV2, 64 queries/head"},
+                   compress={"vectors/s": n * steps / t1, "GB/s": n * 1282 * steps / t1 / 1e9, "TFLOP/s": n * 393216 * steps / t1 / 1e12},
+                   scores={"keys/s": n * steps / t2, "GB/s": n * 1026 * steps / t2 / 1e9, "ms": 1e3 * t2 / steps},
+                   roofline={"bound": "tensor", "achieved": n * 393216 * steps / t1 / 1e12,
+                             "peak": float(peaks.get("bf16_tflops_sustained", 1400.0)), "unit": "TFLOP/s",
+                             "frac": n * 393216 * steps / t1 / 1e12 / float(peaks.get("bf16_tflops_sustained", 1400.0)),
+                             "traffic": None, "note": "FP32 CUDA-core kernels: no tensor-core path for head_dim 256 yet"})
+    else:  # llama
+        nl = args.layers if args.layers != LAYERS else 4
+        idxs = ([0, 1] + list(range(10, 10 + nl)))[:nl] if nl > 2 else list(range(nl))
+        codecs = [tq.TurboQuantV3(HEAD_DIM, key_bits=6, value_bits=4, residual_window=128, layer_idx=l, n_layers=32,
+                                  protected_layers=4, device=dev) for l in idxs]
+        keys, vals = [], []
+        for l in idxs:
+            g = torch.Generator(device=dev).manual_seed(30000 + l)
+            k = torch.randn(8, 8, 32768, HEAD_DIM, generator=g, device=dev, dtype=torch.bfloat16)
+            v = torch.randn(8, 8, 32768, HEAD_DIM, generator=g, device=dev, dtype=torch.bfloat16)
+            k[:, :, :, :4] *= 10.0
+            keys.append(k)
+            vals.append(v)
+        plan = batched.CachePlan(codecs, keys, vals)
+        tq_ = _time_steps(plan.compress, steps, warmup, flush)
+        td_ = _time_steps(plan.decompress, steps, warmup, flush)
+        n = nl * 2 * 8 * 8 * (32768 - 128)
+        by = sum(8 * 8 * (32768 - 128) * (256 + (128 * b + 7) // 8 // (1 if b > 4 else 1) * 0 + (128 // (8 // b)) + 2)
+                 for c in codecs for b in (c.key_bits, c.value_bits))
+        out.update(metric=METRIC, unit="vectors/s", value=n * steps / (tq_ + td_), ms_per_step=1e3 * (tq_ + td_) / steps,
+                   dtype="bf16xbf16->f32",
+                   config={"workload": f"configs[2] shape, {nl} layers (indices {idxs}): (8,8,32768,128) bf16, K6/V4, "
+                                       "residual_window=128, protected_layers=4 at 8 bits"},
+                   roofline={"bound": "hbm", "achieved": by * steps / tq_ / 1e9, "peak": peak, "unit": "GB/s",
+                             "frac": by * steps / tq_ / 1e9 / peak, "traffic": None,
+                             "phases": {"quantize": {"ms": 1e3 * tq_ / steps, "GB/s": by * steps / tq_ / 1e9,
+                                                     "frac": by * steps / tq_ / 1e9 / peak},
+                                        "dequantize": {"ms": 1e3 * td_ / steps, "GB/s": by * steps / td_ / 1e9,
+                                                       "frac": by * steps / td_ / 1e9 / peak}}})
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -155,6 +264,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="kv", choices=["kv", "scores", "qjl", "llama"],
+                    help="kv = the headline workload (configs[1]); the others measure further rows of the path on 1 GPU")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per rank (smaller values are for profiling only)")
     ap.add_argument("--key-bits", type=int, default=KEY_BITS, help="profiling only; the headline workload is K4")
     ap.add_argument("--value-bits", type=int, default=VALUE_BITS, help="profiling only; the headline workload is V2")
@@ -178,6 +289,10 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     lib = _native.lib()
     n_layers = args.layers
+    if args.workload != "kv":
+        if rank == 0:
+            run_side_workload(args, dev)
+        return
 
     kb, vb = args.key_bits, args.value_bits
     codecs = [tq.TurboQuantV3(HEAD_DIM, key_bits=kb, value_bits=vb, residual_window=0, layer_idx=l,

@@ -53,10 +53,11 @@ enum {
 };
 
 #define TQ_MAX_DIM 256
-#define TQ_CODEBOOK_FLOATS 528
-/* A codebook block is 528 floats on the device: [0,L) centroids ascending,
+#define TQ_CODEBOOK_FLOATS 800
+/* A codebook block is 800 floats on the device: [0,L) centroids ascending,
  * [256, 256+L-1) decision thresholds, every other slot below 512 +inf, and
- * [512,528) the parameters of the search shortcut (below).  Threshold k is
+ * [512,528) the parameters of the search shortcut and [528,800) its cell table
+ * (below).  Threshold k is
  * the largest fp32 y for which fl|y-c_k| <= fl|y-c_(k+1)|, so that
  * index(y) = #{k : y > threshold_k} equals the first-minimum argmin over
  * |y - c| evaluated in fp32 (turboquant/compressors_v3.py:60-61).  The identity
@@ -68,8 +69,11 @@ enum {
  * c1, c2, c3.  With t = sat(y*s + 0.5) and e = round(t*(c1 + t*(c2 + t*c3))) the
  * host has verified, in the same fp32 arithmetic, that the exact index is e or
  * e+1 for every y, so index(y) = e + (y > threshold_e): one table look-up instead
- * of a binary search, with the same result.  Built for up to 31 thresholds; when
- * no cubic passes the check the slot [512] is 0 and kernels search.            */
+ * of a binary search, with the same result.  Built for up to 31 thresholds.
+ * For 32..255 thresholds [512] = 2.0: e comes from a byte table over 1024 uniform
+ * cells of t, stored from float slot 528 on, e = table[round(t * 1024)], under the
+ * same verified guarantee.  When neither form passes the check, [512] is 0 and
+ * kernels search.                                                              */
 
 int tq_version(void);
 const char* tq_strerror(int code);

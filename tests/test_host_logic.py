@@ -203,12 +203,21 @@ def test_search_shortcut_parameters_bracket_the_exact_index():
         for bits in range(1, 9):
             block = N.codebook_block(torch.from_numpy(z[f"c_{d}_{bits}"]), bits).numpy().astype(np.float64)
             n = 2 ** bits - 1
-            if bits > 5:
-                assert block[512] == 0.0          # more thresholds than lanes: kernels search instead
+            thr = block[256:256 + n]
+            if bits > 5:                          # more thresholds than lanes: byte table over 1024 cells of t
+                assert block[512] == 2.0 and block[517] == 1024.0, (d, bits)
+                raw = N.codebook_block(torch.from_numpy(z[f"c_{d}_{bits}"]), bits).numpy()
+                cells = raw[528:528 + 257].view(np.uint8)[:1025].astype(np.int64)
+                s = block[513]
+                y = np.concatenate([rng.normal(0, 1 / np.sqrt(d), 50000), np.linspace(-1, 1, 20001), thr,
+                                    np.nextafter(thr.astype(np.float32), np.float32(np.inf)).astype(np.float64)])
+                t = np.clip(y * s + 0.5, 0.0, 1.0)
+                e = cells[np.rint(t * 1024).astype(np.int64)]
+                exact = (y[:, None] > thr[None, :]).sum(axis=1)
+                assert np.all((e == exact) | (e + 1 == exact)), (d, bits)
                 continue
             assert block[512] == 1.0, (d, bits)
             s, c1, c2, c3 = block[513:517]
-            thr = block[256:256 + n]
             y = np.concatenate([rng.normal(0, 1 / np.sqrt(d), 50000), np.linspace(-1, 1, 20001), thr,
                                 np.nextafter(thr.astype(np.float32), np.float32(np.inf)).astype(np.float64)])
             t = np.clip(y * s + 0.5, 0.0, 1.0)

@@ -52,8 +52,80 @@ inline int exact_index(float y, const float* thr, int n) {
 
 // Least-squares cubic through the origin mapping the thresholds to k + 1/2, then an
 // exhaustive check of "exact index is e or e+1" around every threshold and on a grid.
+// Wide codes (more than 31 thresholds): a table over 1024 uniform cells of t = sat(y s + 1/2)
+// gives the lower candidate e; thresholds are at least one cell apart, so the exact index is
+// e or e + 1, which the same exhaustive check confirms.  cell(y) = round(t * 1024).
+constexpr int kCells = 1024;
+inline int cell_of(float y, float s) {
+  float t = fmaf(y, s, 0.5f);
+  if (!(t > 0.f)) t = 0.f;
+  if (t > 1.f) t = 1.f;
+  const float u = fmaf(t, (float)kCells, 8388608.0f);
+  int32_t bits;
+  memcpy(&bits, &u, 4);
+  return bits - 0x4B000000;
+}
+
+void fit_cell_table(float* block, int n) {
+  const float* thr = block + 256;
+  const double lim = fmax(fabs((double)thr[0]), fabs((double)thr[n - 1])) * 1.001 + 1e-12;
+  const float s = (float)(0.5 / lim);
+  uint8_t* cells = reinterpret_cast<uint8_t*>(block + 528);
+  // lower candidate of a cell = exact index at the smallest y that maps to it
+  int c_prev = -1;
+  // walk y upwards through every threshold and every cell boundary by scanning a fine grid, then
+  // fix the table from the thresholds themselves: e[c] = number of thresholds whose cell is < c,
+  // plus those in an earlier cell position; verified below in any case.
+  for (int c = 0; c <= kCells; ++c) cells[c] = 0;
+  (void)c_prev;
+  // count thresholds per cell
+  int per_cell[kCells + 1] = {0};
+  for (int k = 0; k < n; ++k) {
+    const int c = cell_of(thr[k], s);
+    if (c < 0 || c > kCells) return;
+    per_cell[c]++;
+    if (per_cell[c] > 1) return;            // two thresholds in one cell: table cannot bracket
+  }
+  int below = 0;                            // thresholds in cells strictly below c
+  for (int c = 0; c <= kCells; ++c) {
+    if (below > 255) return;
+    cells[c] = (uint8_t)below;              // inside cell c the exact index is `below` or `below + 1`
+    below += per_cell[c];
+  }
+  const float s_lo = s * (1.0f - 4e-6f), s_hi = s * (1.0f + 4e-6f);
+  auto ok_at = [&](float y) {
+    const int i = exact_index(y, thr, n);
+    for (float sv : {s_lo, s, s_hi}) {
+      const int c = cell_of(y, sv);
+      if (c < 0 || c > kCells) return false;
+      const int e = cells[c];
+      if (!((e == i || e + 1 == i) && (e < n || i == e))) return false;
+    }
+    return true;
+  };
+  for (int k = 0; k < n; ++k) {
+    float y = thr[k];
+    for (int step = 0; step < 4; ++step) y = nextafterf(y, -INFINITY);
+    for (int step = 0; step < 9; ++step) {
+      if (!ok_at(y)) return;
+      y = nextafterf(y, INFINITY);
+    }
+  }
+  const int grid = 1 << 18;
+  for (int g = 0; g <= grid; ++g) {
+    const float y = (float)(-1.25 + 2.5 * (double)g / grid);
+    if (!ok_at(y)) return;
+  }
+  const float specials[] = {0.f, -0.f, 1.f, -1.f, 100.f, -100.f, 1000.f, -1000.f, INFINITY, -INFINITY, NAN};
+  for (float y : specials) if (!ok_at(y)) return;
+  block[512] = 2.f;
+  block[513] = s;
+  block[517] = (float)kCells;
+}
+
 void fit_shortcut(float* block, int n) {
   for (int i = 512; i < TQ_CODEBOOK_FLOATS; ++i) block[i] = 0.f;
+  if (n > 31 && n <= 255) { fit_cell_table(block, n); return; }
   if (n < 1 || n > 31) return;
   const float* thr = block + 256;
   const double lim = fmax(fabs((double)thr[0]), fabs((double)thr[n - 1])) * 1.001 + 1e-12;

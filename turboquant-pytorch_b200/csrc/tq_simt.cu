@@ -446,6 +446,153 @@ __global__ void __launch_bounds__(NT) k_score_packed(TqScoreJob job, const float
   }
 }
 
+// y = x @ m for a handful of rows (decode queries): one block per row, one thread per output
+// coordinate, the same sequential-k fma order as the tiled contraction.
+template <int XDT>
+__global__ void k_project_rows(const void* x, int K, const float* __restrict__ m, int N, float* out) {
+  __shared__ float xs[TQ_MAX_DIM];
+  const int64_t row = blockIdx.x;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = load_elem<XDT>(x, row * K + k);
+  __syncthreads();
+  for (int n = threadIdx.x; n < N; n += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < K; ++k) acc = fmaf(xs[k], __ldg(m + (int64_t)k * N + n), acc);
+    out[row * N + n] = acc;
+  }
+}
+
+// head_dim 128 specialisation: eight lanes share a key (16 coordinates = G/8 packed bytes
+// each, so a warp reads four whole rows with one fully coalesced load), the rotated query
+// slice lives in registers, and the only shared-memory traffic is the centroid look-up.
+// After eight iterations lane L of a warp holds the four logits of key L of the warp's 32
+// keys, so logits leave as 128-byte rows and the softmax partials are per lane.
+template <int BITS>
+__global__ void __launch_bounds__(NT) k_score_packed_d128(TqScoreJob job, const float* __restrict__ qrot, float* stats,
+                                                         int nblk) {
+  constexpr int D = 128;
+  constexpr int IPB = 8 / BITS;
+  constexpr int G = D / IPB;
+  constexpr int BPT = G / 8;                     // packed bytes per thread: 2, 4, 8 or 16
+  constexpr unsigned MASK = (1u << BITS) - 1u;
+  __shared__ float cent_s[256];
+  __shared__ float red[NT / 32][RQ];
+  for (int i = threadIdx.x; i < 256; i += NT) cent_s[i] = __ldg(job.codebook + kCentroidOff + i);
+  const int blk = blockIdx.x % nblk;
+  const int64_t bh = blockIdx.x / nblk;
+  const int64_t b = bh / job.Hkv, hkv = bh % job.Hkv;
+  const int rep = (int)(job.Hq / job.Hkv);
+  const int R = rep * (int)job.Sq;
+  const int64_t s_begin = (int64_t)blk * SCORE_KEYS_PER_BLOCK;
+  const int64_t s_end = min(s_begin + SCORE_KEYS_PER_BLOCK, job.Sk);
+  const uint8_t* keys = job.idx_bytes + bh * job.Sk * G;
+  const uint16_t* norms = job.norms + bh * job.Sk;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane & 7, grp = lane >> 3;
+  __syncthreads();
+  for (int r0 = 0; r0 < R; r0 += RQ) {
+    float q[16][RQ];
+    int64_t out_row[RQ];
+#pragma unroll
+    for (int rq = 0; rq < RQ; ++rq) {
+      const int r = r0 + rq;
+      int64_t grow = 0;
+      if (r < R) {
+        const int64_t hq = hkv * rep + r / job.Sq, sq = r % job.Sq;
+        grow = (b * job.Hq + hq) * job.Sq + sq;
+      }
+      out_row[rq] = grow;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) q[e][rq] = (r < R) ? __ldg(qrot + grow * D + sub * 16 + e) : 0.f;
+    }
+    float run_max[RQ], run_sum[RQ];
+#pragma unroll
+    for (int rq = 0; rq < RQ; ++rq) { run_max[rq] = -INFINITY; run_sum[rq] = 0.f; }
+    for (int64_t kb = s_begin + warp * 32; kb < s_end; kb += (NT / 32) * 32) {
+      float keep[RQ] = {0.f, 0.f, 0.f, 0.f};
+      // all eight loads of the round go out before any is consumed
+      constexpr int WPT = (BPT + 3) / 4;
+      uint32_t wall[8][WPT];
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int64_t key = kb + it * 4 + grp;
+#pragma unroll
+        for (int x = 0; x < WPT; ++x) wall[it][x] = 0u;
+        if (key < s_end) {
+          const uint8_t* src = keys + key * G + sub * BPT;
+          if constexpr (BPT == 2) wall[it][0] = *reinterpret_cast<const uint16_t*>(src);
+          else if constexpr (BPT == 4) wall[it][0] = *reinterpret_cast<const uint32_t*>(src);
+          else if constexpr (BPT == 8) { const uint2 v = *reinterpret_cast<const uint2*>(src); wall[it][0] = v.x; wall[it][1] = v.y; }
+          else { const uint4 v = *reinterpret_cast<const uint4*>(src); wall[it][0] = v.x; wall[it][1] = v.y; wall[it][2] = v.z; wall[it][3] = v.w; }
+        }
+      }
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int64_t key = kb + it * 4 + grp;
+        float acc[RQ] = {0.f, 0.f, 0.f, 0.f};
+        if (key < s_end) {
+          const uint32_t* w = wall[it];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const int byte = e / IPB;
+            const int sh = 8 * (byte & 3) + BITS * (IPB - 1 - (e % IPB));
+            const float c = cent_s[(w[byte >> 2] >> sh) & MASK];
+#pragma unroll
+            for (int rq = 0; rq < RQ; ++rq) acc[rq] = fmaf(q[e][rq], c, acc[rq]);
+          }
+        }
+#pragma unroll
+        for (int rq = 0; rq < RQ; ++rq) {
+          float v = acc[rq];
+          v += __shfl_xor_sync(0xffffffffu, v, 4);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          const float g = __shfl_sync(0xffffffffu, v, (lane & 3) * 8);     // key it*4 + (lane & 3)
+          if ((lane >> 2) == it) keep[rq] = g;
+        }
+      }
+      const int64_t key = kb + lane;
+      if (key < s_end) {
+        const float nv = __half2float(__ushort_as_half(norms[key]));
+#pragma unroll
+        for (int rq = 0; rq < RQ; ++rq) {
+          if (r0 + rq < R) {
+            const float l = keep[rq] * nv * job.scale;
+            job.logits[out_row[rq] * job.Sk + key] = l;
+            if (stats != nullptr) {
+              const float m = fmaxf(run_max[rq], l);
+              if (m != -INFINITY) run_sum[rq] = run_sum[rq] * __expf(run_max[rq] - m) + __expf(l - m);
+              run_max[rq] = m;
+            }
+          }
+        }
+      }
+    }
+    if (stats != nullptr) {
+#pragma unroll
+      for (int rq = 0; rq < RQ; ++rq) {
+        const float m = warp_max(run_max[rq]);
+        const float sc = (run_max[rq] == -INFINITY) ? 0.f : run_sum[rq] * __expf(run_max[rq] - m);
+        const float sm = warp_sum(sc);
+        if (lane == 0) red[warp][rq] = m;
+        __syncthreads();
+        float bm = -INFINITY;
+        for (int w = 0; w < NT / 32; ++w) bm = fmaxf(bm, red[w][rq]);
+        __syncthreads();
+        const float contrib = (m == -INFINITY) ? 0.f : sm * __expf(m - bm);
+        if (lane == 0) red[warp][rq] = contrib;
+        __syncthreads();
+        if (threadIdx.x == 0 && r0 + rq < R) {
+          float tot = 0.f;
+          for (int w = 0; w < NT / 32; ++w) tot += red[w][rq];
+          stats[(out_row[rq] * nblk + blk) * 2 + 0] = bm;
+          stats[(out_row[rq] * nblk + blk) * 2 + 1] = tot;
+        }
+        __syncthreads();
+      }
+    }
+  }
+}
+
 // probs = exp(l - M) / Z with (M, Z) folded from the per-block partials.
 __global__ void __launch_bounds__(NT) k_softmax_finish(const float* __restrict__ logits, const float* __restrict__ stats,
                                                       int nblk, int64_t Sk, float* probs) {
@@ -784,6 +931,11 @@ int simt_dequantize(const TqDequantizeJob& job, cudaStream_t st) {
 
 int simt_project(const void* x, int x_dtype, int64_t n, int K, const float* m, int N, float* out, cudaStream_t st) {
   if (n == 0) return TQ_OK;
+  if (n <= 512) {          // few rows: a tile kernel would run on a handful of SMs
+    const int threads = N <= 128 ? 128 : 256;
+    TQ_DISPATCH_DT(x_dtype, k_project_rows<DT_><<<(unsigned)n, threads, 0, st>>>(x, K, m, N, out));
+    return check_launch();
+  }
   const int nj = nj_for(N);
   const size_t smem = sizeof(float) * (TM * lda_for(K) + KC * (64 * nj + BPAD));
   const int grid = grid_for((n + TM - 1) / TM, 2);
@@ -814,7 +966,21 @@ int simt_score_packed(const TqScoreJob& job, cudaStream_t st) {
   int rc = simt_project(job.q, job.q_dtype, rows, job.D, job.rotation_t, job.D, qrot, st);
   if (rc != TQ_OK) return rc;
   const int64_t blocks = job.B * job.Hkv * nblk;
-  k_score_packed<<<(unsigned)blocks, NT, 0, st>>>(job, qrot, job.probs != nullptr ? stats : nullptr, nblk);
+  float* st_ptr = job.probs != nullptr ? stats : nullptr;
+  if (job.D == 128 && ((uintptr_t)job.idx_bytes & 15u) == 0) {
+    switch (job.bits) {
+      case 1: k_score_packed_d128<1><<<(unsigned)blocks, NT, 0, st>>>(job, qrot, st_ptr, nblk); break;
+      case 2: k_score_packed_d128<2><<<(unsigned)blocks, NT, 0, st>>>(job, qrot, st_ptr, nblk); break;
+      case 3: k_score_packed_d128<3><<<(unsigned)blocks, NT, 0, st>>>(job, qrot, st_ptr, nblk); break;
+      case 4: k_score_packed_d128<4><<<(unsigned)blocks, NT, 0, st>>>(job, qrot, st_ptr, nblk); break;
+      case 5: k_score_packed_d128<5><<<(unsigned)blocks, NT, 0, st>>>(job, qrot, st_ptr, nblk); break;
+      case 6: k_score_packed_d128<6><<<(unsigned)blocks, NT, 0, st>>>(job, qrot, st_ptr, nblk); break;
+      case 7: k_score_packed_d128<7><<<(unsigned)blocks, NT, 0, st>>>(job, qrot, st_ptr, nblk); break;
+      default: k_score_packed_d128<8><<<(unsigned)blocks, NT, 0, st>>>(job, qrot, st_ptr, nblk); break;
+    }
+  } else {
+    k_score_packed<<<(unsigned)blocks, NT, 0, st>>>(job, qrot, st_ptr, nblk);
+  }
   rc = check_launch();
   if (rc != TQ_OK || job.probs == nullptr) return rc;
   int chunks = (int)((job.Sk + 16383) / 16384);

@@ -49,8 +49,9 @@ struct Cfg {
   static constexpr uint32_t kPieceOff = BF16 ? 2 * kTileBytes : 0;            // offset of the pieces in the image
   static constexpr uint32_t kOffA = 0;
   static constexpr uint32_t kOffPi = kOffA + kStages * kTileBytes;
-  static constexpr uint32_t kOffThr = kOffPi + kPieces * kTileBytes;          // 4 x 256 floats
-  static constexpr uint32_t kOffBar = kOffThr + 4 * 256 * 4;
+  static constexpr uint32_t kThrRegion = 2560;   // per epilogue warpgroup: 256 thresholds + a 1028-byte cell table
+  static constexpr uint32_t kOffThr = kOffPi + kPieces * kTileBytes;
+  static constexpr uint32_t kOffBar = kOffThr + 4 * kThrRegion;
   static constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;                // + alignment slack
 };
 static_assert(Cfg<false>::kSmemBytes <= 232448 && Cfg<true>::kSmemBytes <= 232448, "shared memory budget");
@@ -438,6 +439,38 @@ __device__ __forceinline__ void quant_row_fast(uint32_t tacc, uint32_t (&a)[16],
   }
 }
 
+// Wide codes (one index per byte): the lower candidate comes from the cell table, then the
+// same saturating-fma compare against that candidate's threshold (stored times 2^40).
+__device__ __forceinline__ void quant_chunk_cells(const uint32_t (&raw)[16], const Shortcut& sc, const float* thr_h,
+                                                  const uint8_t* cells, uint8_t* dst, bool valid) {
+  uint32_t acc[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    const float r = __uint_as_float(raw[e]);
+    float t, pf;
+    asm("fma.rn.sat.f32 %0, %1, %2, 0f3F000000;" : "=f"(t) : "f"(r), "f"(sc.s_inv));
+    const float u = fmaf(t, 1024.0f, 8388608.0f);
+    const uint32_t e0 = cells[__float_as_uint(u) & 0x7FFu];
+    const float th = thr_h[e0];
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(pf) : "f"(r), "f"(sc.h_inv), "f"(-th));
+    const uint32_t idx = e0 + (pf > 0.5f ? 1u : 0u);
+    acc[e >> 2] |= idx << (8 * (e & 3));
+  }
+  if (valid) *reinterpret_cast<uint4*>(dst) = make_uint4(acc[0], acc[1], acc[2], acc[3]);
+}
+
+__device__ __forceinline__ void quant_row_cells(uint32_t tacc, uint32_t (&a)[16], uint32_t (&b)[16], const Shortcut& sc,
+                                                const float* thr_h, const uint8_t* cells, uint8_t* idx_row, bool valid) {
+#pragma unroll 1
+  for (int c = 0; c < 8; c += 2) {
+    tmem_wait16(a); tmem_issue16(tacc + (c + 1) * 16, b);
+    quant_chunk_cells(a, sc, thr_h, cells, idx_row + c * 16, valid);
+    tmem_wait16(b);
+    if (c + 2 < 8) tmem_issue16(tacc + (c + 2) * 16, a);
+    quant_chunk_cells(b, sc, thr_h, cells, idx_row + (c + 1) * 16, valid);
+  }
+}
+
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_constant__ UmmaQuantBatch batch) {
   constexpr int kStages = Cfg<BF16>::kStages;
@@ -584,8 +617,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
     const int wg = ew >> 2;                    // 0..3, also the accumulator this group reads
     const int quarter = warp & 3;              // TMEM lanes this warp may touch: 32*quarter ..
     const int row = quarter * 32 + lane;
-    float* thr = thr_all + wg * 256;
+    float* thr = thr_all + wg * (Cfg<BF16>::kThrRegion / 4);
+    uint8_t* cells = reinterpret_cast<uint8_t*>(thr + 256);
     const int wg_tid = (ew & 3) * 32 + lane;
+    int mode = 0;                               // 0 search, 1 cubic shortcut, 2 cell table
     bool ok = true;
     bool fast = false;
     Shortcut sc = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -594,9 +629,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
       const int t = t0 + i;
       if (view_advance(batch, t, job)) {
         asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");     // previous tile's readers are done
-        thr[wg_tid] = __ldg(job.codebook + kThresholdOff + wg_tid);
-        thr[wg_tid + 128] = __ldg(job.codebook + kThresholdOff + 128 + wg_tid);
-        fast = __ldg(job.codebook + 512) != 0.f && job.bits <= 5;
+        mode = (int)__ldg(job.codebook + 512);
+        if (mode == 2 && job.bits < 5) mode = 0;
+        const float tscale = mode == 2 ? 1099511627776.0f : 1.0f;      // the cell path compares against thr * 2^40
+        thr[wg_tid] = __ldg(job.codebook + kThresholdOff + wg_tid) * tscale;
+        thr[wg_tid + 128] = __ldg(job.codebook + kThresholdOff + 128 + wg_tid) * tscale;
+        if (mode == 2)
+          for (int e = wg_tid; e < 257; e += 128)
+            reinterpret_cast<uint32_t*>(cells)[e] = __float_as_uint(__ldg(job.codebook + 528 + e));
+        fast = mode == 1 && job.bits <= 5;
         sc.s = __ldg(job.codebook + 513);
         sc.c1 = __ldg(job.codebook + 514);
         sc.c2 = __ldg(job.codebook + 515);
@@ -616,11 +657,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
       uint8_t* idx_row = job.idx_out + n * (int64_t)job.g;
       if (!(batch.ablate & 2)) {
         uint32_t ra[16], rb[16];
-        const float ssq = fast ? ssq_row_fast(tacc, ra, rb) : ssq_row_generic(tacc);
+        const float ssq = (fast || mode == 2) ? ssq_row_fast(tacc, ra, rb) : ssq_row_generic(tacc);
         const float norm = __fsqrt_rn(ssq);
         const float inv = __fdiv_rn(1.0f, norm + 1e-8f);
         if (valid) job.norms_out[n] = __half_as_ushort(__float2half_rn(norm));
-        if (fast) {
+        if (mode == 2) {
+          sc.s_inv = sc.s * inv;
+          sc.h_inv = 1099511627776.0f * inv;
+          quant_row_cells(tacc, ra, rb, sc, thr, cells, idx_row, valid);
+        } else if (fast) {
           sc.s_inv = sc.s * inv;
           sc.h_inv = 1099511627776.0f * inv;          // 2^40: exact scaling
           if (batch.ablate & 16) {

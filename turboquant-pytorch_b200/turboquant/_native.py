@@ -17,7 +17,7 @@ LIB_PATH = os.path.join(_HERE, "libturboquant_b200.so")
 
 F32, F16, BF16 = 0, 1, 2
 IDX_PACKED, IDX_U8, IDX_I64 = 0, 1, 2
-CODEBOOK_FLOATS = 528
+CODEBOOK_FLOATS = 800
 SCORE_NOALLOC_SCRATCH_BYTES = 4 << 20
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
