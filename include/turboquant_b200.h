@@ -70,6 +70,8 @@ enum {
  * host has verified, in the same fp32 arithmetic, that the exact index is e or
  * e+1 for every y, so index(y) = e + (y > threshold_e): one table look-up instead
  * of a binary search, with the same result.  Built for up to 31 thresholds.
+ * [518] = 1.0 when a straight line passed the check (c2 = c3 = 0; it does for the
+ * three thresholds of 2-bit codes), which lets kernels skip the two higher terms.
  * For 32..255 thresholds [512] = 2.0: e comes from a byte table over 1024 uniform
  * cells of t, stored from float slot 528 on, e = table[round(t * 1024)], under the
  * same verified guarantee.  When neither form passes the check, [512] is 0 and

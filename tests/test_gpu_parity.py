@@ -429,3 +429,27 @@ def test_cache_plan_equals_per_layer_calls_and_can_rerun():
     plan.compress(); plan.refresh_window(); plan.decompress()
     rk, _ = codecs[0].decompress_kv(*codecs[0].compress_kv(keys[0], vals[0]))
     assert torch.equal(plan.reconstructed[0][0], rk)
+
+
+@pytest.mark.gpu
+def test_host_streamed_cache_equals_per_layer_calls():
+    """Pinned-host round trip pipelined over layer groups: same bytes as per-layer calls, also on reuse."""
+    from turboquant import batched
+    L = 5
+    codecs = [tq.TurboQuantV3(128, key_bits=4, value_bits=2, residual_window=16, layer_idx=l, n_layers=L, protected_layers=1,
+                              device=DEV) for l in range(L)]
+    hk = [O.synthetic_kv((1, 2, 300, 128), torch.float16, 800 + l).pin_memory() for l in range(L)]
+    hv = [O.synthetic_kv((1, 2, 300, 128), torch.float16, 850 + l).pin_memory() for l in range(L)]
+    with pytest.raises(ValueError):
+        batched.HostStreamedCache(codecs, [t.clone() for t in hk], hv, DEV)       # not pinned
+    cache = batched.HostStreamedCache(codecs, hk, hv, DEV, groups=3)
+    for rep in range(2):
+        if rep == 1:                          # new contents in the same pinned tensors: buffers are reused
+            for t in hk + hv:
+                t.mul_(0.75)
+        ok, ov = cache.run()
+        torch.cuda.synchronize()
+        for l in range(L):
+            k, v = hk[l].to(DEV), hv[l].to(DEV)
+            rk, rv = codecs[l].decompress_kv(*codecs[l].compress_kv(k, v))
+            assert torch.equal(ok[l].to(DEV), rk) and torch.equal(ov[l].to(DEV), rv)

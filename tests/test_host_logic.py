@@ -218,6 +218,8 @@ def test_search_shortcut_parameters_bracket_the_exact_index():
                 continue
             assert block[512] == 1.0, (d, bits)
             s, c1, c2, c3 = block[513:517]
+            if block[518] == 1.0:                 # a straight line passed the host check
+                assert c2 == 0.0 and c3 == 0.0 and bits <= 3
             y = np.concatenate([rng.normal(0, 1 / np.sqrt(d), 50000), np.linspace(-1, 1, 20001), thr,
                                 np.nextafter(thr.astype(np.float32), np.float32(np.inf)).astype(np.float64)])
             t = np.clip(y * s + 0.5, 0.0, 1.0)

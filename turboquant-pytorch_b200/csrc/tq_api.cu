@@ -131,8 +131,8 @@ void fit_shortcut(float* block, int n) {
   const double lim = fmax(fabs((double)thr[0]), fabs((double)thr[n - 1])) * 1.001 + 1e-12;
   const float s = (float)(0.5 / lim);
   // basis t, t^2, t^3 ; target k + 0.5 - 0.5 = k  (the constant 1/2 is the rounding offset)
+  auto try_degree = [&](int deg, float& c1, float& c2, float& c3) -> bool {
   double ata[3][3] = {{0}}, atb[3] = {0};
-  const int deg = n >= 3 ? 3 : n;        // fewer thresholds than coefficients: lower degree
   for (int k = 0; k < n; ++k) {
     const double t = (double)thr[k] * (double)s + 0.5;
     const double b[3] = {t, t * t, t * t * t};
@@ -152,7 +152,7 @@ void fit_shortcut(float* block, int n) {
     int piv = i;
     for (int r = i + 1; r < deg; ++r) if (fabs(m[r][i]) > fabs(m[piv][i])) piv = r;
     for (int j = 0; j <= deg; ++j) { double tmp = m[i][j]; m[i][j] = m[piv][j]; m[piv][j] = tmp; }
-    if (fabs(m[i][i]) < 1e-300) return;
+    if (fabs(m[i][i]) < 1e-300) return false;
     for (int r = i + 1; r < deg; ++r) {
       const double f = m[r][i] / m[i][i];
       for (int j = i; j <= deg; ++j) m[r][j] -= f * m[i][j];
@@ -163,7 +163,7 @@ void fit_shortcut(float* block, int n) {
     for (int j = i + 1; j < deg; ++j) acc -= m[i][j] * c[j];
     c[i] = acc / m[i][i];
   }
-  const float c1 = (float)c[0], c2 = (float)c[1], c3 = (float)c[2];
+  c1 = (float)c[0]; c2 = (float)c[1]; c3 = (float)c[2];
   // Kernels may fold the per-vector scale into s, which moves t by an ulp or two; demand the
   // bracket for slightly perturbed scales as well so that such rounding can never matter.
   const float s_lo = s * (1.0f - 4e-6f), s_hi = s * (1.0f + 4e-6f);
@@ -179,22 +179,32 @@ void fit_shortcut(float* block, int n) {
     float y = thr[k];
     for (int step = 0; step < 4; ++step) y = nextafterf(y, -INFINITY);
     for (int step = 0; step < 9; ++step) {
-      if (!ok_at(y)) return;
+      if (!ok_at(y)) return false;
       y = nextafterf(y, INFINITY);
     }
   }
   const int grid = 1 << 16;
   for (int g = 0; g <= grid; ++g) {
     const float y = (float)(-1.25 + 2.5 * (double)g / grid);
-    if (!ok_at(y)) return;
+    if (!ok_at(y)) return false;
   }
   const float specials[] = {0.f, -0.f, 1.f, -1.f, 100.f, -100.f, 1000.f, -1000.f, INFINITY, -INFINITY, NAN};
-  for (float y : specials) if (!ok_at(y)) return;
+  for (float y : specials) if (!ok_at(y)) return false;
+  return true;
+  };
+  // a straight line is tried first (it brackets the few thresholds of 1- and 2-bit codes and
+  // saves two multiply-adds per coordinate), then the cubic
+  float c1 = 0.f, c2 = 0.f, c3 = 0.f;
+  int degree = 0;
+  if (try_degree(1, c1, c2, c3)) degree = 1;
+  else if (try_degree(n >= 3 ? 3 : n, c1, c2, c3)) degree = 3;
+  if (degree == 0) return;
   block[512] = 1.f;
   block[513] = s;
   block[514] = c1;
   block[515] = c2;
   block[516] = c3;
+  block[518] = degree == 1 ? 1.f : 0.f;     // 1: c2 = c3 = 0, kernels may skip those terms
 }
 
 int check_common(int D, int bits) {

@@ -163,6 +163,12 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
       : "memory");
 }
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0u;
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -346,7 +352,7 @@ struct Shortcut {
 
 // CH coordinates (16 here) per step: the loop body stays small enough to live in the
 // instruction cache while four warps per scheduler run it out of phase.
-template <int BITS, int CH, bool NOSHFL = false>
+template <int BITS, int CH, bool NOSHFL = false, bool LINEAR = false>
 __device__ __forceinline__ void quant_chunk_fast(const uint32_t (&raw)[CH], const Shortcut& sc, uint8_t* dst,
                                                  bool valid) {
   constexpr int IPB = 8 / BITS;
@@ -365,9 +371,14 @@ __device__ __forceinline__ void quant_chunk_fast(const uint32_t (&raw)[CH], cons
     const float r = __uint_as_float(raw[e]);
     float t, pf;
     asm("fma.rn.sat.f32 %0, %1, %2, 0f3F000000;" : "=f"(t) : "f"(r), "f"(sc.s_inv));
-    float q = fmaf(sc.c3, t, sc.c2);
-    q = fmaf(q, t, sc.c1);
-    const float u = fmaf(q, t, 8388608.0f);
+    float u;
+    if constexpr (LINEAR) {                      // c2 = c3 = 0: the same value as the cubic form below
+      u = fmaf(sc.c1, t, 8388608.0f);
+    } else {
+      float q = fmaf(sc.c3, t, sc.c2);
+      q = fmaf(q, t, sc.c1);
+      u = fmaf(q, t, 8388608.0f);
+    }
     const float thr_h = NOSHFL ? sc.thr_lane_h : __shfl_sync(0xffffffffu, sc.thr_lane_h, __float_as_int(u));
     asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(pf) : "f"(r), "f"(sc.h_inv), "f"(-thr_h));
     const float ui = u + pf;
@@ -425,17 +436,17 @@ __device__ __forceinline__ float ssq_row_fast(uint32_t tacc, uint32_t (&a)[16], 
   return ssq;       // step 0 is in flight into `a`
 }
 
-template <int BITS, bool NOSHFL = false>
+template <int BITS, bool NOSHFL = false, bool LINEAR = false>
 __device__ __forceinline__ void quant_row_fast(uint32_t tacc, uint32_t (&a)[16], uint32_t (&b)[16], const Shortcut& sc,
                                                uint8_t* idx_row, bool valid) {
   constexpr int BYTES = 16 / (8 / BITS);
 #pragma unroll 1
   for (int c = 0; c < 8; c += 2) {
     tmem_wait16(a); tmem_issue16(tacc + (c + 1) * 16, b);
-    quant_chunk_fast<BITS, 16, NOSHFL>(a, sc, idx_row + c * BYTES, valid);
+    quant_chunk_fast<BITS, 16, NOSHFL, LINEAR>(a, sc, idx_row + c * BYTES, valid);
     tmem_wait16(b);
     if (c + 2 < 8) tmem_issue16(tacc + (c + 2) * 16, a);
-    quant_chunk_fast<BITS, 16, NOSHFL>(b, sc, idx_row + (c + 1) * BYTES, valid);
+    quant_chunk_fast<BITS, 16, NOSHFL, LINEAR>(b, sc, idx_row + (c + 1) * BYTES, valid);
   }
 }
 
@@ -566,47 +577,52 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the loop and the waits, so that tile counters and descriptor
+    // bases are computed in converged code; one elected lane issues the MMAs and the commits.
+    {
       int pi_uses = 0;
       bool ok = true;
       QuantJobView job;
+      const uint32_t idesc = idesc_f16(BF16);
+      const uint64_t b_base = smem_desc_sw128(pi_smem);
       for (int i = 0; i < n_local && ok; ++i) {
         const int t = t0 + i;
         if (view_advance(batch, t, job)) {
           ok = mbar_wait(bar_pifull, (uint32_t)(pi_uses & 1), abort_flag);
-          if (!ok) break;
           ++pi_uses;
         }
         const int s = i % kStages, b = i % kAccBufs;
-        ok = mbar_wait(bar_full + 8 * s, (uint32_t)((i / kStages) & 1), abort_flag);
-        if (!ok) break;
-        ok = mbar_wait(bar_tempty + 8 * b, (uint32_t)(((i / kAccBufs) & 1) ^ 1), abort_flag);
+        ok = ok && mbar_wait(bar_full + 8 * s, (uint32_t)((i / kStages) & 1), abort_flag);
+        ok = ok && mbar_wait(bar_tempty + 8 * b, (uint32_t)(((i / kAccBufs) & 1) ^ 1), abort_flag);
+        ok = __all_sync(0xffffffffu, ok);        // lanes leave the loop together
         if (!ok) break;
         tc_fence_after();
-        // One thread issues all MMAs, so the issue loop must stay a handful of instructions per
-        // MMA or the tensor pipe starves: descriptors are a per-tile base plus compile-time
-        // offsets (the start-address field counts 16-byte units and cannot carry out).
-        const uint32_t idesc = idesc_f16(BF16);
+        // The issue loop must stay a handful of instructions per MMA or the tensor pipe
+        // starves: descriptors are a per-tile base plus compile-time offsets (the
+        // start-address field counts 16-byte units and cannot carry out).
         const uint32_t d_tmem = tmem_base + (uint32_t)(b * 128);
         const uint64_t a_base = smem_desc_sw128(a_smem + s * kTileBytes);
-        const uint64_t b_base = smem_desc_sw128(pi_smem);
-        if (!(batch.ablate & 4)) {
+        const bool last_of_job = i + 1 >= n_local || t + 1 >= job.end;
+        if (elect_one()) {
+          if (!(batch.ablate & 4)) {
 #pragma unroll
-          for (int piece = 0; piece < kPieces; ++piece) {
+            for (int piece = 0; piece < kPieces; ++piece) {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              constexpr uint32_t kUnit = 16;
-              const uint64_t koff = (uint64_t)(((k >> 2) * kHalfBytes + (k & 3) * 32) / kUnit);
-              const uint64_t poff = (uint64_t)((piece * kTileBytes) / kUnit);
-              umma_f16(d_tmem, a_base + koff, b_base + poff + koff, idesc, (piece | k) != 0 ? 1u : 0u);
+              for (int k = 0; k < 8; ++k) {
+                constexpr uint32_t kUnit = 16;
+                const uint64_t koff = (uint64_t)(((k >> 2) * kHalfBytes + (k & 3) * 32) / kUnit);
+                const uint64_t poff = (uint64_t)((piece * kTileBytes) / kUnit);
+                umma_f16(d_tmem, a_base + koff, b_base + poff + koff, idesc, (piece | k) != 0 ? 1u : 0u);
+              }
             }
           }
+          if (batch.ablate & 128) mbar_arrive(bar_tfull + 8 * b); else
+          umma_commit(bar_tfull + 8 * b);      // one commit per tile: the epilogue and the producer both wait on it
+          if (last_of_job) umma_commit(bar_pifree);
         }
-        if (batch.ablate & 128) mbar_arrive(bar_tfull + 8 * b); else
-        umma_commit(bar_tfull + 8 * b);      // one commit per tile: the epilogue and the producer both wait on it
-        if (i + 1 >= n_local || t + 1 >= job.end) umma_commit(bar_pifree);    // last tile of this job here
+        __syncwarp();
       }
-      if (!ok) {
+      if (!ok && lane == 0) {
         *abort_flag = 1;
         if (batch.status != nullptr) atomicCAS(batch.status, 0, (2 << 16) | (int)blockIdx.x);
       }
@@ -622,7 +638,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
     const int wg_tid = (ew & 3) * 32 + lane;
     int mode = 0;                               // 0 search, 1 cubic shortcut, 2 cell table
     bool ok = true;
-    bool fast = false;
+    bool fast = false, linear = false;
     Shortcut sc = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     QuantJobView job;
     for (int i = wg; i < n_local && ok; i += 4) {
@@ -638,6 +654,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
           for (int e = wg_tid; e < 257; e += 128)
             reinterpret_cast<uint32_t*>(cells)[e] = __float_as_uint(__ldg(job.codebook + 528 + e));
         fast = mode == 1 && job.bits <= 5;
+        linear = __ldg(job.codebook + 518) == 1.0f;
         sc.s = __ldg(job.codebook + 513);
         sc.c1 = __ldg(job.codebook + 514);
         sc.c2 = __ldg(job.codebook + 515);
@@ -657,11 +674,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
       uint8_t* idx_row = job.idx_out + n * (int64_t)job.g;
       if (!(batch.ablate & 2)) {
         uint32_t ra[16], rb[16];
-        const float ssq = (fast || mode == 2) ? ssq_row_fast(tacc, ra, rb) : ssq_row_generic(tacc);
+        float ssq;
+        if (batch.ablate & 512) { ssq = 1.0f; if (fast || mode == 2) tmem_issue16(tacc, ra); }
+        else ssq = (fast || mode == 2) ? ssq_row_fast(tacc, ra, rb) : ssq_row_generic(tacc);
         const float norm = __fsqrt_rn(ssq);
         const float inv = __fdiv_rn(1.0f, norm + 1e-8f);
         if (valid) job.norms_out[n] = __half_as_ushort(__float2half_rn(norm));
-        if (mode == 2) {
+        if (batch.ablate & 256) {
+          if (fast || mode == 2) tmem_wait16(ra);
+        } else if (mode == 2) {
           sc.s_inv = sc.s * inv;
           sc.h_inv = 1099511627776.0f * inv;
           quant_row_cells(tacc, ra, rb, sc, thr, cells, idx_row, valid);
@@ -673,9 +694,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
             else quant_row_fast<2, true>(tacc, ra, rb, sc, idx_row, valid);
           } else
           switch (job.bits) {
-            case 1: quant_row_fast<1>(tacc, ra, rb, sc, idx_row, valid); break;
-            case 2: quant_row_fast<2>(tacc, ra, rb, sc, idx_row, valid); break;
-            case 3: quant_row_fast<3>(tacc, ra, rb, sc, idx_row, valid); break;
+            case 1:
+              if (linear) quant_row_fast<1, false, true>(tacc, ra, rb, sc, idx_row, valid);
+              else quant_row_fast<1>(tacc, ra, rb, sc, idx_row, valid);
+              break;
+            case 2:
+              if (linear) quant_row_fast<2, false, true>(tacc, ra, rb, sc, idx_row, valid);
+              else quant_row_fast<2>(tacc, ra, rb, sc, idx_row, valid);
+              break;
+            case 3:
+              if (linear) quant_row_fast<3, false, true>(tacc, ra, rb, sc, idx_row, valid);
+              else quant_row_fast<3>(tacc, ra, rb, sc, idx_row, valid);
+              break;
             case 4: quant_row_fast<4>(tacc, ra, rb, sc, idx_row, valid); break;
             default: quant_row_fast<5>(tacc, ra, rb, sc, idx_row, valid); break;
           }

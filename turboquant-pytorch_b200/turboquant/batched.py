@@ -115,6 +115,79 @@ class CachePlan:
                     full[:, :, cut:, :].copy_(comp["fp16"])
 
 
+class HostStreamedCache:
+    """Round trip of a KV cache that lives in pinned host memory, pipelined over PCIe.
+
+    The layers are split into groups.  Each group has its own device staging tensors and
+    CachePlan; three streams carry host->device copies, the two kernels and device->host
+    copies, so that group g is being quantised and dequantised while group g+1 arrives
+    and group g-1 leaves (the link is full duplex).  Results are those of CachePlan on
+    the same tensors.  run() returns once everything is enqueued; the calling stream waits
+    for the last copy, so ordinary stream semantics hold for the caller.
+    """
+
+    def __init__(self, codecs: Sequence[TurboQuantV3], host_keys: Sequence[torch.Tensor],
+                 host_values: Sequence[torch.Tensor], device, groups: int = 6):
+        if not all(t.is_pinned() for t in list(host_keys) + list(host_values)):
+            raise ValueError("HostStreamedCache needs pinned host tensors")
+        self.device = torch.device(device)
+        n = len(codecs)
+        groups = max(1, min(groups, n))
+        self.host_keys, self.host_values = list(host_keys), list(host_values)
+        self.host_out_keys = [torch.empty_like(t).pin_memory() for t in host_keys]
+        self.host_out_values = [torch.empty_like(t).pin_memory() for t in host_values]
+        self.dev_keys = [torch.empty(t.shape, dtype=t.dtype, device=self.device) for t in host_keys]
+        self.dev_values = [torch.empty(t.shape, dtype=t.dtype, device=self.device) for t in host_values]
+        self.bounds = [(n * g // groups, n * (g + 1) // groups) for g in range(groups)]
+        self.plans = [CachePlan(codecs[a:b], self.dev_keys[a:b], self.dev_values[a:b]) for a, b in self.bounds]
+        self._windows = any(c.residual_window > 0 for c in codecs)
+        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
+        mk = lambda: [torch.cuda.Event() for _ in self.bounds]
+        self.ev_in, self.ev_packed, self.ev_run, self.ev_out = mk(), mk(), mk(), mk()
+        self._ran = False
+        self.h2d_bytes = sum(t.numel() * t.element_size() for t in self.host_keys + self.host_values)
+        self.d2h_bytes = self.h2d_bytes
+
+    @torch.no_grad()
+    def run(self):
+        """Copy in, compress, decompress, copy out; returns the pinned output tensors."""
+        cur = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(cur)
+        for st in (self.s_in, self.s_run, self.s_out):
+            st.wait_event(start)
+        for g, (a, b) in enumerate(self.bounds):
+            plan = self.plans[g]
+            with torch.cuda.stream(self.s_in):
+                if self._ran:
+                    self.s_in.wait_event(self.ev_packed[g])      # last run's quantize has read the staging tensors
+                for l in range(a, b):
+                    self.dev_keys[l].copy_(self.host_keys[l], non_blocking=True)
+                    self.dev_values[l].copy_(self.host_values[l], non_blocking=True)
+                self.ev_in[g].record(self.s_in)
+            with torch.cuda.stream(self.s_run):
+                self.s_run.wait_event(self.ev_in[g])
+                if self._ran:
+                    self.s_run.wait_event(self.ev_out[g])        # last run's outputs have left the device
+                plan.compress()
+                self.ev_packed[g].record(self.s_run)
+                if self._windows:
+                    plan.refresh_window()
+                plan.decompress()
+                self.ev_run[g].record(self.s_run)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(self.ev_run[g])
+                for i, l in enumerate(range(a, b)):
+                    rk, rv = plan.reconstructed[i]
+                    self.host_out_keys[l].copy_(rk, non_blocking=True)
+                    self.host_out_values[l].copy_(rv, non_blocking=True)
+                self.ev_out[g].record(self.s_out)
+        self._ran = True
+        for st in (self.s_in, self.s_run, self.s_out):
+            cur.wait_stream(st)
+        return self.host_out_keys, self.host_out_values
+
+
 def shard_units(n_layers: int, n_kv_heads: int, rank: int, world: int):
     """(layer, kv_head) units owned by `rank`: contiguous blocks of the layer-major unit list.
 
