@@ -163,6 +163,27 @@ def _time_steps(fn, steps, warmup, flush):
     return sum(a.elapsed_time(b) for a, b in evs) * 1e-3
 
 
+def directional_ceilings(flush):
+    """Read-only, write-only and copy bandwidth (GB/s) of this GPU, measured with plain torch kernels over the
+    256 MiB flush buffer: a write-dominated kernel cannot reach the copy figure the roofline is quoted against."""
+    n = flush.numel()
+    half = n // 2
+    def best(fn, reps=5):
+        for _ in range(2):
+            fn()
+        t = 1e30
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            t = min(t, a.elapsed_time(b) * 1e-3)
+        return t
+    tw = best(lambda: flush.zero_())
+    tr = best(lambda: flush.view(torch.float32).sum())
+    tc = best(lambda: flush[half:].copy_(flush[:half]))
+    return {"read_only": n / tr / 1e9, "write_only": n / tw / 1e9, "copy": 2 * half / tc / 1e9}
+
+
 def run_side_workload(args, dev):
     """Other rows of the path, measured with the same hygiene; one JSON line each.
 
@@ -380,6 +401,13 @@ def main():
     peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
     ach_q = bytes_q * args.steps / t_q / 1e9
     ach_d = bytes_d * args.steps / t_d / 1e9
+    # one-directional ceilings: quantize mostly reads (16-bit vectors in), dequantize mostly writes
+    ceil = directional_ceilings(flush)
+    big = n_layers * KV_HEADS * SEQ * 2 * HEAD_DIM * 2          # 16-bit vectors, K and V
+    small = bytes_q - big                                        # packed rows + norms
+    def floor_ms(rd, wr):
+        return 1e3 * max(rd / ceil["read_only"], wr / ceil["write_only"], (rd + wr) / ceil["copy"]) / 1e9
+    floor_q, floor_d = floor_ms(big, small), floor_ms(small, big)
     dominant = ("quantize", ach_q, t_q) if t_q >= t_d else ("dequantize", ach_d, t_d)
     out = {
         "metric": METRIC, "value": world * vectors_per_step * args.steps / t_all, "unit": "vectors/s", "n_gpus": world,
@@ -396,9 +424,15 @@ def main():
                      "traffic_source": "ncu dram__bytes_read+write of an 18-layer capture x2 (profiles/)",
                      "peak_source": peak_src,
                      "phases": {"quantize": {"GB/s": ach_q, "frac": ach_q / peak_gbs, "ms": 1e3 * t_q / args.steps,
-                                             "algorithmic_bytes": bytes_q},
+                                             "algorithmic_bytes": bytes_q, "directional_floor_ms": floor_q,
+                                             "frac_of_directional_floor": floor_q / (1e3 * t_q / args.steps)},
                                 "dequantize": {"GB/s": ach_d, "frac": ach_d / peak_gbs, "ms": 1e3 * t_d / args.steps,
-                                               "algorithmic_bytes": bytes_d}}},
+                                               "algorithmic_bytes": bytes_d, "directional_floor_ms": floor_d,
+                                               "frac_of_directional_floor": floor_d / (1e3 * t_d / args.steps)}},
+                     "directional_ceilings_GBs": ceil,
+                     "directional_note": "read-only / write-only / copy bandwidth measured in this run with torch "
+                                         "kernels; floor = max(read bytes / read-only, write bytes / write-only, "
+                                         "all bytes / copy)"},
         "e2e": {"value": world * vectors_per_step * e2e_steps / t_e2e, "unit": "vectors/s",
                 "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes, "steps": e2e_steps,
                 "ms_per_step": 1e3 * t_e2e / e2e_steps,

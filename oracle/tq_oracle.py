@@ -338,6 +338,67 @@ class V3Oracle:
                 "key_bits": self.key_bits, "value_bits": self.value_bits}
 
 
+class V3CacheOracle:
+    """The incremental cache the reference's generation harness wraps around TurboQuantV3
+    (turboquant/generation_test_v2.py:48-166), without the transformers base class: a list of
+    compressed chunks plus a list of recent 16-bit tokens per layer; every update decompresses
+    all chunks and concatenates."""
+
+    def __init__(self, key_bits=4, value_bits=2, residual_window=128, protected_layers=0, n_layers=36):
+        self.key_bits, self.value_bits = key_bits, value_bits
+        self.residual_window = residual_window
+        self.protected_layers, self.n_layers = protected_layers, n_layers
+        self._codec, self._chunks, self._recent = {}, {}, {}
+        self._total, self._compressed = {}, {}
+        self._codebooks = {}
+
+    def update(self, key_states, value_states, layer_idx):
+        """generation_test_v2.py:80-152."""
+        d = key_states.shape[-1]
+        if layer_idx not in self._codec:                      # :64-78, residual_window=0 inside the codec
+            self._codec[layer_idx] = V3Oracle(d, self.key_bits, self.value_bits, residual_window=0,
+                                              layer_idx=layer_idx, n_layers=self.n_layers,
+                                              protected_layers=self.protected_layers, seed=42,
+                                              codebook_cache=self._codebooks)
+            self._chunks[layer_idx], self._recent[layer_idx] = [], []
+            self._total[layer_idx] = self._compressed[layer_idx] = 0
+        codec = self._codec[layer_idx]
+        self._total[layer_idx] += key_states.shape[2]
+        self._recent[layer_idx].append((key_states, value_states))
+        rk = torch.cat([k for k, _ in self._recent[layer_idx]], dim=2)
+        rv = torch.cat([v for _, v in self._recent[layer_idx]], dim=2)
+        rw = self.residual_window
+        if rw == 0:                                           # :104-112
+            if rk.shape[2] > 0:
+                self._chunks[layer_idx].append(codec.compress_kv(rk, rv))
+                self._compressed[layer_idx] += rk.shape[2]
+                self._recent[layer_idx] = []
+        elif rk.shape[2] > rw:                                # :113-127
+            over = rk.shape[2] - rw
+            self._chunks[layer_idx].append(codec.compress_kv(rk[:, :, :over, :], rv[:, :, :over, :]))
+            self._compressed[layer_idx] += over
+            self._recent[layer_idx] = [(rk[:, :, over:, :], rv[:, :, over:, :])]
+        parts_k, parts_v = [], []                             # :129-146
+        for ck, cv in self._chunks[layer_idx]:
+            dk, dv = codec.decompress_kv(ck, cv)
+            parts_k.append(dk.to(key_states.dtype))
+            parts_v.append(dv.to(value_states.dtype))
+        if self._recent[layer_idx]:
+            parts_k.append(torch.cat([k for k, _ in self._recent[layer_idx]], dim=2))
+            parts_v.append(torch.cat([v for _, v in self._recent[layer_idx]], dim=2))
+        return torch.cat(parts_k, dim=2), torch.cat(parts_v, dim=2)
+
+    def get_seq_length(self, layer_idx=0):
+        return self._total.get(layer_idx, 0)
+
+    def get_compression_info(self):
+        """generation_test_v2.py:157-165."""
+        if not self._compressed:
+            return "no compression"
+        comp, total = self._compressed.get(0, 0), self._total.get(0, 0)
+        return f"{comp} compressed, {total - comp} fp16, {total} total"
+
+
 def v3_scores(queries: torch.Tensor, keys_recon: torch.Tensor) -> torch.Tensor:
     """Attention logits on reconstructed keys.  turboquant/validate_v3.py:86-87.
 

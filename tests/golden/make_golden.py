@@ -32,7 +32,13 @@ def sha(t: torch.Tensor) -> str:
     return hashlib.sha256(t.contiguous().numpy().tobytes()).hexdigest()
 
 
+ONLY = None     # with --only: the fixture files to (re)write; the others are computed but left untouched
+
+
 def save(name: str, **arrays):
+    if ONLY is not None and name not in ONLY:
+        print(f"{name}: kept")
+        return
     path = os.path.join(HERE, name)
     np.savez_compressed(path, **arrays)
     print(f"{name}: {os.path.getsize(path) / 1024:.1f} KiB")
@@ -41,7 +47,10 @@ def save(name: str, **arrays):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only", nargs="*", default=None, help="rewrite only these fixture files")
     args = ap.parse_args()
+    global ONLY
+    ONLY = set(args.only) if args.only else None
     sys.path.insert(0, args.reference)
     import turboquant as ref  # the reference package
     from turboquant.lloyd_max import solve_lloyd_max, LloydMaxCodebook
@@ -235,6 +244,25 @@ def main():
     logits = torch.matmul(q.float(), rep.transpose(-2, -1))
     save("scores.npz", keys=bits16(keys), q=q.numpy(), idx=c["idx_bytes"].numpy(), norms=bits16(c["vec_norms"]),
          logits=logits.numpy(), probs=torch.softmax(logits, dim=-1).numpy())
+
+    # ---- 10. incremental cache of the generation harness (prefill + decode steps) ----
+    from turboquant.generation_test_v2 import V3Cache
+    out = {}
+    for tag, rw, prefill, steps in (("w", 16, 150, 10), ("z", 0, 40, 3)):
+        cache = V3Cache(key_bits=4, value_bits=2, residual_window=rw, protected_layers=1, n_layers=4)
+        for layer in (0, 1):                       # layer 0 is protected (8 bits), layer 1 is not
+            total = prefill + steps
+            k = synthetic_kv((1, 2, total, 128), torch.float16, 61000 + 10 * layer + rw)
+            v = synthetic_kv((1, 2, total, 128), torch.float16, 62000 + 10 * layer + rw)
+            fk, fv = cache.update(k[:, :, :prefill], v[:, :, :prefill], layer)
+            out[f"{tag}{layer}_prefill_k"], out[f"{tag}{layer}_prefill_v"] = bits16(fk), bits16(fv)
+            for t in range(prefill, total):
+                fk, fv = cache.update(k[:, :, t:t + 1], v[:, :, t:t + 1], layer)
+            out[f"{tag}{layer}_k"], out[f"{tag}{layer}_v"] = bits16(k), bits16(v)
+            out[f"{tag}{layer}_full_k"], out[f"{tag}{layer}_full_v"] = bits16(fk), bits16(fv)
+            out[f"{tag}{layer}_len"] = np.int64(cache.get_seq_length(layer))
+        out[f"{tag}_info"] = np.array(cache.get_compression_info())
+    save("v3_cache.npz", **out)
 
 
 if __name__ == "__main__":

@@ -453,3 +453,37 @@ def test_host_streamed_cache_equals_per_layer_calls():
             k, v = hk[l].to(DEV), hv[l].to(DEV)
             rk, rv = codecs[l].decompress_kv(*codecs[l].compress_kv(k, v))
             assert torch.equal(ok[l].to(DEV), rk) and torch.equal(ov[l].to(DEV), rv)
+
+
+@pytest.mark.gpu
+def test_incremental_cache_matches_reference_harness():
+    """turboquant.cache.V3Cache against outputs of the reference's V3Cache (prefill, then one token per step)."""
+    from turboquant.cache import V3Cache
+    z = load_golden("v3_cache.npz")
+
+    def frac_off(got, want, tol=2e-3):
+        g, w = got.float().cpu(), want.float()
+        return float(((g - w).abs() > tol * float(w.abs().max())).float().mean())
+
+    for tag, rw, prefill in (("w", 16, 150), ("z", 0, 40)):
+        cache = V3Cache(key_bits=4, value_bits=2, residual_window=rw, protected_layers=1, n_layers=4, initial_capacity=64)
+        for layer in (0, 1):
+            k = from_bits16(z[f"{tag}{layer}_k"], torch.float16).to(DEV)
+            v = from_bits16(z[f"{tag}{layer}_v"], torch.float16).to(DEV)
+            total = k.shape[2]
+            fk, fv = cache.update(k[:, :, :prefill], v[:, :, :prefill], layer)
+            assert frac_off(fk, from_bits16(z[f"{tag}{layer}_prefill_k"], torch.float16)) <= 1e-4
+            assert frac_off(fv, from_bits16(z[f"{tag}{layer}_prefill_v"], torch.float16)) <= 1e-4
+            for t in range(prefill, total):       # the buffer grows past its initial capacity on the way
+                fk, fv = cache.update(k[:, :, t:t + 1], v[:, :, t:t + 1], layer)
+            assert fk.shape == (1, 2, total, 128) and fk.dtype == torch.float16
+            assert frac_off(fk, from_bits16(z[f"{tag}{layer}_full_k"], torch.float16)) <= 1e-4
+            assert frac_off(fv, from_bits16(z[f"{tag}{layer}_full_v"], torch.float16)) <= 1e-4
+            if rw:
+                assert torch.equal(fk[:, :, -rw:], k[:, :, -rw:])
+            assert cache.get_seq_length(layer) == int(z[f"{tag}{layer}_len"])
+            ck, cv = cache.packed_chunks(layer)
+            assert sum(c["shape"][2] for c in ck) == total - (rw if rw else 0)
+            mem = cache.memory_bytes(layer)
+            assert mem["fp16_bytes"] == 2 * 2 * total * 128 * 2 and mem["compression_ratio"] > 1.5
+        assert cache.get_compression_info() == str(z[f"{tag}_info"])

@@ -262,3 +262,32 @@ def test_pack_layout_msb_first():
     assert pad == 0 and p.tolist() == [[200, 3]]
     p, pad = O.pack_indices(np.array([[1, 0, 1]]), 1)
     assert pad == 5 and p.tolist() == [[0b10100000]]
+
+
+def _frac_off(got, want, tol=2e-3):
+    """Fraction of elements further than tol * max|want| from the fixture (an index that flips moves one element)."""
+    g, w = got.float(), want.float()
+    return float(((g - w).abs() > tol * float(w.abs().max())).float().mean())
+
+
+def test_v3_cache_prefill_and_decode_steps():
+    """The incremental cache of the generation harness: same tokens in, same full K/V out after every phase."""
+    z = load_golden("v3_cache.npz")
+    for tag, rw, prefill in (("w", 16, 150), ("z", 0, 40)):
+        cache = O.V3CacheOracle(key_bits=4, value_bits=2, residual_window=rw, protected_layers=1, n_layers=4)
+        for layer in (0, 1):
+            k = from_bits16(z[f"{tag}{layer}_k"], torch.float16)
+            v = from_bits16(z[f"{tag}{layer}_v"], torch.float16)
+            total = k.shape[2]
+            fk, fv = cache.update(k[:, :, :prefill], v[:, :, :prefill], layer)
+            assert _frac_off(fk, from_bits16(z[f"{tag}{layer}_prefill_k"], torch.float16)) <= 1e-4
+            assert _frac_off(fv, from_bits16(z[f"{tag}{layer}_prefill_v"], torch.float16)) <= 1e-4
+            for t in range(prefill, total):
+                fk, fv = cache.update(k[:, :, t:t + 1], v[:, :, t:t + 1], layer)
+            assert fk.shape == (1, 2, total, 128) and fk.dtype == torch.float16
+            assert _frac_off(fk, from_bits16(z[f"{tag}{layer}_full_k"], torch.float16)) <= 1e-4
+            assert _frac_off(fv, from_bits16(z[f"{tag}{layer}_full_v"], torch.float16)) <= 1e-4
+            if rw:                                  # the window tokens pass through untouched
+                assert torch.equal(fk[:, :, -rw:], k[:, :, -rw:])
+            assert cache.get_seq_length(layer) == int(z[f"{tag}{layer}_len"])
+        assert cache.get_compression_info() == str(z[f"{tag}_info"])

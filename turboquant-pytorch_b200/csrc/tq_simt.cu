@@ -456,27 +456,80 @@ __global__ void k_project_rows(const void* x, int K, const float* __restrict__ m
   __syncthreads();
   for (int n = threadIdx.x; n < N; n += blockDim.x) {
     float acc = 0.f;
-    for (int k = 0; k < K; ++k) acc = fmaf(xs[k], __ldg(m + (int64_t)k * N + n), acc);
+    int k = 0;
+    for (; k + 32 <= K; k += 32) {               // 32 independent loads in flight, then the ordered fma chain
+      float mv[32];
+#pragma unroll
+      for (int u = 0; u < 32; ++u) mv[u] = __ldg(m + (int64_t)(k + u) * N + n);
+#pragma unroll
+      for (int u = 0; u < 32; ++u) acc = fmaf(xs[k + u], mv[u], acc);
+    }
+    for (; k < K; ++k) acc = fmaf(xs[k], __ldg(m + (int64_t)k * N + n), acc);
     out[row * N + n] = acc;
   }
 }
 
-// head_dim 128 specialisation: eight lanes share a key (16 coordinates = G/8 packed bytes
-// each, so a warp reads four whole rows with one fully coalesced load), the rotated query
-// slice lives in registers, and the only shared-memory traffic is the centroid look-up.
-// After eight iterations lane L of a warp holds the four logits of key L of the warp's 32
-// keys, so logits leave as 128-byte rows and the softmax partials are per lane.
+// head_dim 128 specialisation: a thread owns whole keys (two at a time, 64 keys per warp and
+// round), so no partial sums cross lanes.  The packed row is read in 16-byte pieces; for every
+// coordinate the centroid comes from a shared look-up (byte offsets prepared a word at a
+// time, so the load is [register + constant]) and the four rotated query values of that
+// coordinate come from one broadcast 16-byte shared load, used for both keys.  Lane L holds
+// the logits of keys L and L + 32 of the round, so logits leave as 128-byte rows and the
+// softmax partials are per lane.
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+
+// Shared-memory addresses of the centroids of the CPW coordinates packed in one 32-bit word,
+// in coordinate order.  `base` is the shared address of the table, aligned to 1024 bytes, so
+// it can be merged into the byte offsets (index * 4) by the same permute / logic instruction
+// that isolates them: no separate address addition per look-up.
+template <int BITS>
+__device__ __forceinline__ void word_offsets(uint32_t x, uint32_t base, uint32_t (&off)[4 * (8 / BITS)]) {
+  constexpr int IPB = 8 / BITS;
+  constexpr int CPW = 4 * IPB;
+  constexpr uint32_t MASK = (1u << BITS) - 1u;
+  if constexpr (BITS == 4) {
+    const uint32_t even = (x >> 2) & 0x3C3C3C3Cu, odd = (x << 2) & 0x3C3C3C3Cu;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      off[2 * k] = __byte_perm(even, base, 0x7650u | k);       // byte k of `even` under bytes 1..3 of base
+      off[2 * k + 1] = __byte_perm(odd, base, 0x7650u | k);
+    }
+  } else if constexpr (BITS == 2) {
+    const uint32_t f0 = (x >> 4) & 0x0C0C0C0Cu, f1 = (x >> 2) & 0x0C0C0C0Cu, f2 = x & 0x0C0C0C0Cu, f3 = (x << 2) & 0x0C0C0C0Cu;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      off[4 * k] = __byte_perm(f0, base, 0x7650u | k);
+      off[4 * k + 1] = __byte_perm(f1, base, 0x7650u | k);
+      off[4 * k + 2] = __byte_perm(f2, base, 0x7650u | k);
+      off[4 * k + 3] = __byte_perm(f3, base, 0x7650u | k);
+    }
+  } else {
+#pragma unroll
+    for (int u = 0; u < CPW; ++u) {
+      const int byte = u / IPB;
+      const int sh = 8 * byte + BITS * (IPB - 1 - (u % IPB));
+      off[u] = (sh >= 2 ? ((x >> (sh - 2)) & (MASK << 2)) : ((x << (2 - sh)) & (MASK << 2))) | base;
+    }
+  }
+}
+
 template <int BITS>
 __global__ void __launch_bounds__(NT) k_score_packed_d128(TqScoreJob job, const float* __restrict__ qrot, float* stats,
                                                          int nblk) {
   constexpr int D = 128;
   constexpr int IPB = 8 / BITS;
-  constexpr int G = D / IPB;
-  constexpr int BPT = G / 8;                     // packed bytes per thread: 2, 4, 8 or 16
-  constexpr unsigned MASK = (1u << BITS) - 1u;
-  __shared__ float cent_s[256];
+  constexpr int G = D / IPB;                     // packed bytes per key: 16, 32, 64 or 128
+  constexpr int PIECES = G / 16;                 // 16-byte pieces per key
+  constexpr int CPW = 4 * IPB;                   // coordinates per 32-bit word
+  __shared__ __align__(1024) float cent_s[256];
+  __shared__ float4 q_s[D];
   __shared__ float red[NT / 32][RQ];
   for (int i = threadIdx.x; i < 256; i += NT) cent_s[i] = __ldg(job.codebook + kCentroidOff + i);
+  const uint32_t cent_base = (uint32_t)__cvta_generic_to_shared(cent_s);
   const int blk = blockIdx.x % nblk;
   const int64_t bh = blockIdx.x / nblk;
   const int64_t b = bh / job.Hkv, hkv = bh % job.Hkv;
@@ -487,10 +540,7 @@ __global__ void __launch_bounds__(NT) k_score_packed_d128(TqScoreJob job, const 
   const uint8_t* keys = job.idx_bytes + bh * job.Sk * G;
   const uint16_t* norms = job.norms + bh * job.Sk;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int sub = lane & 7, grp = lane >> 3;
-  __syncthreads();
   for (int r0 = 0; r0 < R; r0 += RQ) {
-    float q[16][RQ];
     int64_t out_row[RQ];
 #pragma unroll
     for (int rq = 0; rq < RQ; ++rq) {
@@ -501,67 +551,62 @@ __global__ void __launch_bounds__(NT) k_score_packed_d128(TqScoreJob job, const 
         grow = (b * job.Hq + hq) * job.Sq + sq;
       }
       out_row[rq] = grow;
-#pragma unroll
-      for (int e = 0; e < 16; ++e) q[e][rq] = (r < R) ? __ldg(qrot + grow * D + sub * 16 + e) : 0.f;
     }
+    __syncthreads();                             // the previous group's readers of q_s are done
+#pragma unroll
+    for (int rq = 0; rq < RQ; ++rq)
+      for (int e = threadIdx.x; e < D; e += NT)
+        reinterpret_cast<float*>(q_s)[e * RQ + rq] = (r0 + rq < R) ? __ldg(qrot + out_row[rq] * D + e) : 0.f;
+    __syncthreads();
     float run_max[RQ], run_sum[RQ];
 #pragma unroll
     for (int rq = 0; rq < RQ; ++rq) { run_max[rq] = -INFINITY; run_sum[rq] = 0.f; }
-    for (int64_t kb = s_begin + warp * 32; kb < s_end; kb += (NT / 32) * 32) {
-      float keep[RQ] = {0.f, 0.f, 0.f, 0.f};
-      // all eight loads of the round go out before any is consumed
-      constexpr int WPT = (BPT + 3) / 4;
-      uint32_t wall[8][WPT];
+    for (int64_t kb = s_begin + warp * 64; kb < s_end; kb += (NT / 32) * 64) {
+      const int64_t key_a = kb + lane, key_b = kb + 32 + lane;
+      const bool ok_a = key_a < s_end, ok_b = key_b < s_end;
+      const uint4* src_a = reinterpret_cast<const uint4*>(keys + (ok_a ? key_a : s_begin) * G);
+      const uint4* src_b = reinterpret_cast<const uint4*>(keys + (ok_b ? key_b : s_begin) * G);
+      float acc_a[RQ] = {0.f, 0.f, 0.f, 0.f}, acc_b[RQ] = {0.f, 0.f, 0.f, 0.f};
+      uint4 cur_a = __ldg(src_a), cur_b = __ldg(src_b);
+#pragma unroll 1
+      for (int pc = 0; pc < PIECES; ++pc) {
+        uint4 nxt_a = cur_a, nxt_b = cur_b;
+        if (pc + 1 < PIECES) { nxt_a = __ldg(src_a + pc + 1); nxt_b = __ldg(src_b + pc + 1); }
+        const float4* qp = q_s + pc * 4 * CPW;
+        const uint32_t wa[4] = {cur_a.x, cur_a.y, cur_a.z, cur_a.w};
+        const uint32_t wb[4] = {cur_b.x, cur_b.y, cur_b.z, cur_b.w};
 #pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int64_t key = kb + it * 4 + grp;
+        for (int w = 0; w < 4; ++w) {
+          uint32_t oa[CPW], ob[CPW];
+          word_offsets<BITS>(wa[w], cent_base, oa);
+          word_offsets<BITS>(wb[w], cent_base, ob);
 #pragma unroll
-        for (int x = 0; x < WPT; ++x) wall[it][x] = 0u;
-        if (key < s_end) {
-          const uint8_t* src = keys + key * G + sub * BPT;
-          if constexpr (BPT == 2) wall[it][0] = *reinterpret_cast<const uint16_t*>(src);
-          else if constexpr (BPT == 4) wall[it][0] = *reinterpret_cast<const uint32_t*>(src);
-          else if constexpr (BPT == 8) { const uint2 v = *reinterpret_cast<const uint2*>(src); wall[it][0] = v.x; wall[it][1] = v.y; }
-          else { const uint4 v = *reinterpret_cast<const uint4*>(src); wall[it][0] = v.x; wall[it][1] = v.y; wall[it][2] = v.z; wall[it][3] = v.w; }
-        }
-      }
-#pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int64_t key = kb + it * 4 + grp;
-        float acc[RQ] = {0.f, 0.f, 0.f, 0.f};
-        if (key < s_end) {
-          const uint32_t* w = wall[it];
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int byte = e / IPB;
-            const int sh = 8 * (byte & 3) + BITS * (IPB - 1 - (e % IPB));
-            const float c = cent_s[(w[byte >> 2] >> sh) & MASK];
-#pragma unroll
-            for (int rq = 0; rq < RQ; ++rq) acc[rq] = fmaf(q[e][rq], c, acc[rq]);
+          for (int u = 0; u < CPW; ++u) {
+            const float4 q = qp[w * CPW + u];
+            const float ca = lds_f32(oa[u]), cb = lds_f32(ob[u]);
+            acc_a[0] = fmaf(q.x, ca, acc_a[0]); acc_a[1] = fmaf(q.y, ca, acc_a[1]);
+            acc_a[2] = fmaf(q.z, ca, acc_a[2]); acc_a[3] = fmaf(q.w, ca, acc_a[3]);
+            acc_b[0] = fmaf(q.x, cb, acc_b[0]); acc_b[1] = fmaf(q.y, cb, acc_b[1]);
+            acc_b[2] = fmaf(q.z, cb, acc_b[2]); acc_b[3] = fmaf(q.w, cb, acc_b[3]);
           }
         }
-#pragma unroll
-        for (int rq = 0; rq < RQ; ++rq) {
-          float v = acc[rq];
-          v += __shfl_xor_sync(0xffffffffu, v, 4);
-          v += __shfl_xor_sync(0xffffffffu, v, 2);
-          v += __shfl_xor_sync(0xffffffffu, v, 1);
-          const float g = __shfl_sync(0xffffffffu, v, (lane & 3) * 8);     // key it*4 + (lane & 3)
-          if ((lane >> 2) == it) keep[rq] = g;
-        }
+        cur_a = nxt_a; cur_b = nxt_b;
       }
-      const int64_t key = kb + lane;
-      if (key < s_end) {
-        const float nv = __half2float(__ushort_as_half(norms[key]));
 #pragma unroll
-        for (int rq = 0; rq < RQ; ++rq) {
-          if (r0 + rq < R) {
-            const float l = keep[rq] * nv * job.scale;
-            job.logits[out_row[rq] * job.Sk + key] = l;
-            if (stats != nullptr) {
-              const float m = fmaxf(run_max[rq], l);
-              if (m != -INFINITY) run_sum[rq] = run_sum[rq] * __expf(run_max[rq] - m) + __expf(l - m);
-              run_max[rq] = m;
+      for (int half = 0; half < 2; ++half) {
+        const int64_t key = half ? key_b : key_a;
+        if (half ? ok_b : ok_a) {
+          const float nv = __half2float(__ushort_as_half(norms[key]));
+#pragma unroll
+          for (int rq = 0; rq < RQ; ++rq) {
+            if (r0 + rq < R) {
+              const float l = (half ? acc_b[rq] : acc_a[rq]) * nv * job.scale;
+              job.logits[out_row[rq] * job.Sk + key] = l;
+              if (stats != nullptr) {
+                const float m = fmaxf(run_max[rq], l);
+                if (m != -INFINITY) run_sum[rq] = run_sum[rq] * __expf(run_max[rq] - m) + __expf(l - m);
+                run_max[rq] = m;
+              }
             }
           }
         }
