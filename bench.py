@@ -190,6 +190,7 @@ def run_side_workload(args, dev):
     scores: configs[3] (decode logits + softmax straight from 4-bit packed keys, 32 query heads on 8 KV heads,
             131072 keys per head, one launch set per layer instance);
     qjl:    configs[4] (V2 MSE+QJL compress, then asymmetric scores for 64 queries per head, head_dim 256);
+    decode: the incremental cache (turboquant.cache.V3Cache) in a generation loop: context 8192, one token per step;
     llama:  configs[2] shape per layer ((8, 8, 32768, 128) bf16, K6/V4, window 128, protected layers at 8 bits),
             `--layers` layers of it (two protected, the rest not).
     """
@@ -246,6 +247,32 @@ def run_side_workload(args, dev):
                              "peak": float(peaks.get("bf16_tflops_sustained", 1400.0)), "unit": "TFLOP/s",
                              "frac": n * 393216 * steps / t1 / 1e12 / float(peaks.get("bf16_tflops_sustained", 1400.0)),
                              "traffic": None, "note": "FP32 CUDA-core kernels: no tensor-core path for head_dim 256 yet"})
+    elif args.workload == "decode":
+        # generation loop on the incremental cache: prefill 8192 tokens per layer, then one token per step
+        from turboquant.cache import V3Cache
+        nl = args.layers
+        ctx = SEQ
+        cache = V3Cache(key_bits=KEY_BITS, value_bits=VALUE_BITS, residual_window=128, protected_layers=0, n_layers=nl,
+                        initial_capacity=ctx + 4096)
+        g = torch.Generator(device=dev).manual_seed(70000)
+        for l in range(nl):
+            k = torch.randn(1, KV_HEADS, ctx, HEAD_DIM, generator=g, device=dev).half()
+            cache.update(k, k * 0.5, l)
+        toks = [torch.randn(1, KV_HEADS, 1, HEAD_DIM, generator=g, device=dev).half() for _ in range(8)]
+        it = [0]
+        def step():
+            t = toks[it[0] % len(toks)]
+            it[0] += 1
+            for l in range(nl):
+                cache.update(t, t, l)
+        t = _time_steps(step, steps, warmup, flush)
+        out.update(metric="decode-step cache updates/s (one new token appended to every layer, oldest window token "
+                          "quantised and reconstructed in place)", unit="layer-updates/s", value=nl * steps / t,
+                   ms_per_step=1e3 * t / steps, dtype="f16xf16->f32",
+                   config={"workload": f"incremental cache, {nl} layers x {KV_HEADS} KV heads, context {ctx}, K4/V2, "
+                                       "residual_window=128; host-side call overhead included"},
+                   roofline={"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None,
+                             "traffic": None, "note": "latency path: two small launches per layer"})
     else:  # llama
         nl = args.layers if args.layers != LAYERS else 4
         idxs = ([0, 1] + list(range(10, 10 + nl)))[:nl] if nl > 2 else list(range(nl))
@@ -285,7 +312,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="kv", choices=["kv", "scores", "qjl", "llama"],
+    ap.add_argument("--workload", default="kv", choices=["kv", "scores", "qjl", "llama", "decode"],
                     help="kv = the headline workload (configs[1]); the others measure further rows of the path on 1 GPU")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per rank (smaller values are for profiling only)")
     ap.add_argument("--key-bits", type=int, default=KEY_BITS, help="profiling only; the headline workload is K4")
