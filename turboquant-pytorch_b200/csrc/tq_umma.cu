@@ -23,6 +23,8 @@
 
 #include <atomic>
 #include <cstdlib>
+#include <cstring>
+#include <vector>
 
 #include "tq_common.cuh"
 #include "tq_internal.h"
@@ -1340,11 +1342,22 @@ int umma_quantize(const TqQuantizeJob* jobs, int n_jobs, cudaStream_t st) {
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return TQ_ELAUNCH;
   static thread_local UmmaQuantBatch batch;      // large: keep it off the stack
+  // A caller with static buffers submits the same job array every step: the prepared launch
+  // description (tensor maps included) of this thread's previous call is reused when the
+  // array, the device and the switches are unchanged.  Per-thread, so calls stay re-entrant.
+  static thread_local std::vector<unsigned char> last_jobs;
+  static thread_local int last_dev = -1, last_ablate = 0, last_grid = 0;
+  int cur_dev = 0;
+  cudaGetDevice(&cur_dev);
+  const size_t job_bytes = (size_t)n_jobs * sizeof(TqQuantizeJob);
+  const bool reuse = n_jobs <= kMaxJobs && last_dev == cur_dev && last_ablate == ablate_flags() &&
+                     last_jobs.size() == job_bytes && memcmp(last_jobs.data(), jobs, job_bytes) == 0;
+  last_dev = -1;                                 // invalid until this call has rebuilt or reused the batch
   int done = 0;
   while (done < n_jobs) {
     const int take = (n_jobs - done) < kMaxJobs ? (n_jobs - done) : kMaxJobs;
     int64_t tile_cursor = 0;
-    for (int i = 0; i < take; ++i) {
+    for (int i = 0; i < take && !reuse; ++i) {
       const TqQuantizeJob& j = jobs[done + i];
       UmmaQuantJob& u = batch.jobs[i];
       const int64_t tps = (j.S + kTileRows - 1) / kTileRows;
@@ -1374,26 +1387,34 @@ int umma_quantize(const TqQuantizeJob* jobs, int n_jobs, cudaStream_t st) {
       tile_cursor += tps * j.B * j.H;
       if (tile_cursor >= ((int64_t)1 << 30)) return TQ_ETOOBIG;
     }
-    batch.n_jobs = take;
-    batch.total_tiles = (int32_t)tile_cursor;
-    batch.ablate = ablate_flags();
-    void* status_ptr = nullptr;
-    cudaGetSymbolAddress(&status_ptr, g_umma_status);
-    batch.status = reinterpret_cast<int32_t*>(status_ptr);
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int grid = (int)(tile_cursor < sms ? tile_cursor : sms);
+    int grid = last_grid;
     const bool bf16 = jobs[done].x_dtype == TQ_BF16;
     const uint32_t smem = bf16 ? Cfg<true>::kSmemBytes : Cfg<false>::kSmemBytes;
-    cudaError_t e = bf16 ? cudaFuncSetAttribute(k_umma_quantize<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                         : cudaFuncSetAttribute(k_umma_quantize<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) { note_cuda_error((int)e); return TQ_ELAUNCH; }
+    if (!reuse) {
+      batch.n_jobs = take;
+      batch.total_tiles = (int32_t)tile_cursor;
+      batch.ablate = ablate_flags();
+      void* status_ptr = nullptr;
+      cudaGetSymbolAddress(&status_ptr, g_umma_status);
+      batch.status = reinterpret_cast<int32_t*>(status_ptr);
+      int sms = 148;
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, cur_dev);
+      grid = (int)(tile_cursor < sms ? tile_cursor : sms);
+      cudaError_t e = bf16 ? cudaFuncSetAttribute(k_umma_quantize<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                           : cudaFuncSetAttribute(k_umma_quantize<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) { note_cuda_error((int)e); return TQ_ELAUNCH; }
+    }
     if (bf16) k_umma_quantize<true><<<grid, kThreads, smem, st>>>(batch);
     else k_umma_quantize<false><<<grid, kThreads, smem, st>>>(batch);
     int rc = check_launch();
     if (rc != TQ_OK) return rc;
+    last_grid = grid;
     done += take;
+  }
+  if (n_jobs <= kMaxJobs) {
+    if (!reuse) last_jobs.assign(reinterpret_cast<const unsigned char*>(jobs), reinterpret_cast<const unsigned char*>(jobs) + job_bytes);
+    last_ablate = ablate_flags();
+    last_dev = cur_dev;
   }
   return TQ_OK;
 }
@@ -1416,11 +1437,20 @@ int umma_dequantize(const TqDequantizeJob* jobs, int n_jobs, cudaStream_t st) {
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return TQ_ELAUNCH;
   static thread_local UmmaDeqBatch batch;
+  // same reuse of the previous call's launch description as in umma_quantize
+  static thread_local std::vector<unsigned char> last_jobs;
+  static thread_local int last_dev = -1, last_ablate = 0, last_grid = 0;
+  int cur_dev = 0;
+  cudaGetDevice(&cur_dev);
+  const size_t job_bytes = (size_t)n_jobs * sizeof(TqDequantizeJob);
+  const bool reuse = n_jobs <= kMaxDeqJobs && last_dev == cur_dev && last_ablate == ablate_flags() &&
+                     last_jobs.size() == job_bytes && memcmp(last_jobs.data(), jobs, job_bytes) == 0;
+  last_dev = -1;
   int done = 0;
   while (done < n_jobs) {
     const int take = (n_jobs - done) < kMaxDeqJobs ? (n_jobs - done) : kMaxDeqJobs;
     int64_t tile_cursor = 0;
-    for (int i = 0; i < take; ++i) {
+    for (int i = 0; i < take && !reuse; ++i) {
       const TqDequantizeJob& j = jobs[done + i];
       UmmaDeqJob& u = batch.jobs[i];
       const int64_t tps = (j.S + kTileRows - 1) / kTileRows;
@@ -1453,22 +1483,26 @@ int umma_dequantize(const TqDequantizeJob* jobs, int n_jobs, cudaStream_t st) {
       tile_cursor += tps * j.B * j.H;
       if (tile_cursor >= ((int64_t)1 << 30)) return TQ_ETOOBIG;
     }
-    batch.n_jobs = take;
-    batch.total_tiles = (int32_t)tile_cursor;
-    batch.ablate = ablate_flags();
-    void* status_ptr = nullptr;
-    cudaGetSymbolAddress(&status_ptr, g_umma_status);
-    batch.status = reinterpret_cast<int32_t*>(status_ptr);
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int grid = (int)(tile_cursor < sms ? tile_cursor : sms);
+    int grid = last_grid;
+    if (!reuse) {
+      batch.n_jobs = take;
+      batch.total_tiles = (int32_t)tile_cursor;
+      batch.ablate = ablate_flags();
+      void* status_ptr = nullptr;
+      cudaGetSymbolAddress(&status_ptr, g_umma_status);
+      batch.status = reinterpret_cast<int32_t*>(status_ptr);
+      int sms = 148;
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, cur_dev);
+      grid = (int)(tile_cursor < sms ? tile_cursor : sms);
+    }
     const bool out32 = jobs[done].out_dtype == TQ_F32;
     bool narrow = true;
     for (int i = 0; i < take; ++i) narrow = narrow && jobs[done + i].bits <= 4;
     auto launch = [&](auto kern, uint32_t smem, int threads) -> int {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) { note_cuda_error((int)e); return TQ_ELAUNCH; }
+      if (!reuse) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { note_cuda_error((int)e); return TQ_ELAUNCH; }
+      }
       kern<<<grid, threads, smem, st>>>(batch);
       return TQ_OK;
     };
@@ -1480,7 +1514,13 @@ int umma_dequantize(const TqDequantizeJob* jobs, int n_jobs, cudaStream_t st) {
     if (lrc != TQ_OK) return lrc;
     int rc = check_launch();
     if (rc != TQ_OK) return rc;
+    last_grid = grid;
     done += take;
+  }
+  if (n_jobs <= kMaxDeqJobs) {
+    if (!reuse) last_jobs.assign(reinterpret_cast<const unsigned char*>(jobs), reinterpret_cast<const unsigned char*>(jobs) + job_bytes);
+    last_ablate = ablate_flags();
+    last_dev = cur_dev;
   }
   return TQ_OK;
 }
