@@ -37,7 +37,7 @@ WORKLOAD = ("configs[1]: Qwen2.5-3B-shaped KV cache, 36 layers x 2 KV heads x se
 
 # dram__bytes_read.sum + dram__bytes_write.sum per full 72-job launch, from the ncu captures summarised in
 # profiles/ (18 layers captured, doubled: traffic grows in proportion to the vectors processed)
-NCU_DRAM_BYTES_PER_LAUNCH = {"quantize": 338.0e6, "dequantize": 244.4e6}
+NCU_DRAM_BYTES_PER_LAUNCH = {"quantize": 336.7e6, "dequantize": 246.2e6}
 
 
 def algorithmic_bytes_per_vector(bits: int, elem_bytes: int = 2) -> int:
