@@ -487,3 +487,26 @@ def test_incremental_cache_matches_reference_harness():
             mem = cache.memory_bytes(layer)
             assert mem["fp16_bytes"] == 2 * 2 * total * 128 * 2 and mem["compression_ratio"] > 1.5
         assert cache.get_compression_info() == str(z[f"{tag}_info"])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("d,sq,sk,bh", [(128, 70, 1000, 6), (256, 5, 129, 3), (128, 1, 128, 2)])
+def test_v2_scores_tensor_core_shapes(d, sq, sk, bh):
+    """Asymmetric scores on the tensor-core path: several query blocks, ragged key tiles, both head_dims;
+    checked against the oracle and against the FP32 kernels (TQ_FORCE_SIMT=1)."""
+    import os
+    x = O.synthetic_kv((1, bh, sk, d), torch.float16, seed=52000 + d + sq, outlier_channels=0)
+    q = torch.randn(1, bh, sq, d, generator=torch.Generator().manual_seed(sq))
+    comp = tq.TurboQuantCompressorV2(d, 3, seed=5, device=DEV)
+    c = comp.compress(x.to(DEV))
+    sc = comp.asymmetric_attention_scores(q.to(DEV), c)
+    want = O.v2_scores(q, {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in c.items()}, comp.S.cpu())
+    assert sc.shape == (1, bh, sq, sk) and rel_err(sc, want) <= 1e-5
+    os.environ["TQ_FORCE_SIMT"] = "1"
+    try:
+        sc_simt = comp.asymmetric_attention_scores(q.to(DEV), c)
+    finally:
+        del os.environ["TQ_FORCE_SIMT"]
+    assert rel_err(sc, sc_simt) <= 1e-5
+    from turboquant import _native
+    assert _native.lib().tq_last_device_status() == 0

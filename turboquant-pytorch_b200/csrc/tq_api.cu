@@ -279,7 +279,10 @@ int tq_prepare_rotation_image(const float* m, int D, void* image, void* stream) 
   return tq::umma_prepare_rotation_image(m, D, image, (cudaStream_t)stream);
 }
 
-int tq_last_device_status(void) { return tq::umma_device_status(); }
+int tq_last_device_status(void) {
+  const int a = tq::umma_device_status();
+  return a != 0 ? a : tq::umma_qjl_device_status();
+}
 
 int tq_quantize_rotated(const float* y, int64_t n, int D, int bits, const float* codebook, int idx_mode, void* out,
                         void* stream) {
@@ -403,7 +406,7 @@ int tq_qjl_compress(const TqQjlCompressJob* job, void* stream) {
 
 size_t tq_qjl_scores_workspace_bytes(int64_t BH, int64_t Sq, int D) {
   if (BH < 0 || Sq < 0 || D < 1) return 0;
-  return tq::simt_qjl_scores_workspace(BH, Sq, D);
+  return tq::simt_qjl_scores_workspace(BH, Sq, D) + tq::umma_qjl_scores_image_bytes(BH, Sq, D);
 }
 
 int tq_qjl_scores(const TqQjlScoreJob* job, void* stream) {
@@ -416,7 +419,17 @@ int tq_qjl_scores(const TqQjlScoreJob* job, void* stream) {
       job->qjl_t == nullptr || job->scores == nullptr || job->workspace == nullptr)
     return TQ_ENULL;
   if (((uintptr_t)job->workspace & 15u) != 0) return TQ_EALIGN;
-  if (job->workspace_bytes < tq::simt_qjl_scores_workspace(job->BH, job->Sq, job->D)) return TQ_EWORKSPACE;
+  const size_t simt_ws = tq::simt_qjl_scores_workspace(job->BH, job->Sq, job->D);
+  if (job->workspace_bytes < simt_ws) return TQ_EWORKSPACE;
+  if (tq::umma_qjl_scores_eligible(*job)) {
+    const size_t img = tq::umma_qjl_scores_image_bytes(job->BH, job->Sq, job->D);
+    if (job->workspace_bytes < simt_ws + img) return TQ_EWORKSPACE;
+    const float* qf = nullptr;
+    const float* qproj = nullptr;
+    int rc = tq::simt_qjl_queries(*job, &qf, &qproj, (cudaStream_t)stream);
+    if (rc != TQ_OK) return rc;
+    return tq::umma_qjl_scores(*job, qf, qproj, reinterpret_cast<char*>(job->workspace) + simt_ws, (cudaStream_t)stream);
+  }
   return tq::simt_qjl_scores(*job, (cudaStream_t)stream);
 }
 

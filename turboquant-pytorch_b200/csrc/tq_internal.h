@@ -1,6 +1,7 @@
 // Internal launch interface between the C ABI layer and the kernel files.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include "../../include/turboquant_b200.h"
@@ -23,6 +24,8 @@ int simt_score_packed(const TqScoreJob& job, cudaStream_t st);
 int simt_qjl_compress(const TqQjlCompressJob& job, cudaStream_t st);
 size_t simt_qjl_scores_workspace(int64_t BH, int64_t Sq, int D);
 int simt_qjl_scores(const TqQjlScoreJob& job, cudaStream_t st);
+// fp32 queries and their S-projection, laid out in the job's workspace (qf aliases job.q for fp32 queries)
+int simt_qjl_queries(const TqQjlScoreJob& job, const float** qf, const float** qproj, cudaStream_t st);
 int simt_prod_inner_product(const float* y, int64_t ny, const int64_t* idx, const float* signs, const float* rnorm,
                             int64_t n, int D, int M, const float* rotation, const float* codebook, const float* qjl_t,
                             float* out, void* workspace, cudaStream_t st);
@@ -36,5 +39,16 @@ int umma_quantize(const TqQuantizeJob* jobs, int n_jobs, cudaStream_t st);
 bool umma_dequantize_eligible(const TqDequantizeJob& job);
 int umma_dequantize(const TqDequantizeJob* jobs, int n_jobs, cudaStream_t st);
 int umma_device_status();
+// cuTensorMapEncodeTiled looked up through the runtime (no link-time dependency on libcuda); NULL if unavailable
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                      CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+TensorMapEncodeFn tensor_map_encoder();
+
+// tensor-core asymmetric scores of the MSE+QJL representation (tq_qjl_umma.cu)
+bool umma_qjl_scores_eligible(const TqQjlScoreJob& job);
+size_t umma_qjl_scores_image_bytes(int64_t BH, int64_t Sq, int D);
+int umma_qjl_scores(const TqQjlScoreJob& job, const float* qf, const float* qproj, void* images, cudaStream_t st);
+int umma_qjl_device_status();
 
 }  // namespace tq

@@ -1055,20 +1055,33 @@ size_t simt_qjl_scores_workspace(int64_t BH, int64_t Sq, int D) {
   return (size_t)2 * BH * Sq * D * sizeof(float);   // projected queries + room for upcast queries
 }
 
-int simt_qjl_scores(const TqQjlScoreJob& job, cudaStream_t st) {
-  if (job.BH == 0 || job.Sq == 0 || job.Sk == 0) return TQ_OK;
+int simt_qjl_queries(const TqQjlScoreJob& job, const float** qf_out, const float** qproj_out, cudaStream_t st) {
   float* qproj = reinterpret_cast<float*>(job.workspace);
   const int64_t nq = job.BH * job.Sq;
   int rc = simt_project(job.q, job.q_dtype, nq, job.D, job.qjl_t, job.D, qproj, st);
   if (rc != TQ_OK) return rc;
+  const float* qf = reinterpret_cast<const float*>(job.q);
   if (job.q_dtype != TQ_F32) {
-    float* qf = qproj + nq * job.D;
+    float* up = qproj + nq * job.D;
     int g = grid_for((nq * job.D + 255) / 256, 8);
-    if (job.q_dtype == TQ_F16) k_upcast<TQ_F16><<<g, 256, 0, st>>>(job.q, nq * job.D, qf);
-    else k_upcast<TQ_BF16><<<g, 256, 0, st>>>(job.q, nq * job.D, qf);
+    if (job.q_dtype == TQ_F16) k_upcast<TQ_F16><<<g, 256, 0, st>>>(job.q, nq * job.D, up);
+    else k_upcast<TQ_BF16><<<g, 256, 0, st>>>(job.q, nq * job.D, up);
     rc = check_launch();
     if (rc != TQ_OK) return rc;
+    qf = up;
   }
+  *qf_out = qf;
+  *qproj_out = qproj;
+  return TQ_OK;
+}
+
+int simt_qjl_scores(const TqQjlScoreJob& job, cudaStream_t st) {
+  if (job.BH == 0 || job.Sq == 0 || job.Sk == 0) return TQ_OK;
+  const float* qf_unused = nullptr;
+  const float* qproj_c = nullptr;
+  int rc = simt_qjl_queries(job, &qf_unused, &qproj_c, st);
+  if (rc != TQ_OK) return rc;
+  const float* qproj = qproj_c;
   const int nj = nj_for((int)(job.Sq < 256 ? job.Sq : 256));
   const size_t smem = sizeof(float) * (TM * lda_for(job.D) + KC * (64 * nj + BPAD) + 64 * nj * (TM + 1));
   const int64_t tiles = job.BH * ((job.Sk + TM - 1) / TM);
