@@ -89,15 +89,17 @@ __device__ __forceinline__ uint32_t idesc_f16_n(uint32_t n) {
 // Query image of one unit: row n = query q0 + n of head bh (zero past Sq), contraction index
 // j < D -> Q[n][j], j >= D -> corr * (S Q)[n][j - D]; value = hi + lo in fp16.  Stored as
 // [piece][chunk][row n][64 columns], rows of 128 bytes, 16-byte chunk c at c ^ (n & 7).
+constexpr int kImageSplit = 16;               // blocks per unit in the image kernel
 template <int D>
 __global__ void k_qjl_query_image(const float* __restrict__ qf, const float* __restrict__ qproj, float corr, int64_t Sq,
                                   int n_qblocks, uint8_t* __restrict__ images) {
   constexpr int kChunks = QCfg<D>::kChunks;
-  const int unit = blockIdx.x;
+  const int unit = blockIdx.x / kImageSplit, part = blockIdx.x % kImageSplit;
   const int64_t bh = unit / n_qblocks;
   const int q0 = (unit % n_qblocks) * kQ;
   uint16_t* img = reinterpret_cast<uint16_t*>(images + (size_t)unit * QCfg<D>::kImageBytes);
-  for (int e = threadIdx.x; e < kQ * 2 * D; e += blockDim.x) {
+  constexpr int kPer = kQ * 2 * D / kImageSplit;
+  for (int e = part * kPer + threadIdx.x; e < (part + 1) * kPer; e += blockDim.x) {
     const int n = e / (2 * D), j = e % (2 * D);
     float v = 0.f;
     if (q0 + n < Sq) {
@@ -404,7 +406,7 @@ int launch(const TqQjlScoreJob& job, const float* qf, const float* qproj, uint8_
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { note_cuda_error(100000 + (int)r); return TQ_ELAUNCH; }
   const float corr = (float)(1.2533141373155001 / (double)D);   // sqrt(pi/2) / m with m = D
-  k_qjl_query_image<D><<<(unsigned)units, 256, 0, st>>>(qf, qproj, corr, job.Sq, n_qblocks, images);
+  k_qjl_query_image<D><<<(unsigned)(units * kImageSplit), 256, 0, st>>>(qf, qproj, corr, job.Sq, n_qblocks, images);
   int rc = check_launch();
   if (rc != TQ_OK) return rc;
   batch.rnorm = job.rnorm;

@@ -446,26 +446,39 @@ __global__ void __launch_bounds__(NT) k_score_packed(TqScoreJob job, const float
   }
 }
 
-// y = x @ m for a handful of rows (decode queries): one block per row, one thread per output
-// coordinate, the same sequential-k fma order as the tiled contraction.
-template <int XDT>
-__global__ void k_project_rows(const void* x, int K, const float* __restrict__ m, int N, float* out) {
-  __shared__ float xs[TQ_MAX_DIM];
-  const int64_t row = blockIdx.x;
-  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = load_elem<XDT>(x, row * K + k);
+// y = x @ m for up to a few thousand rows (queries): one block per RPB rows, one thread per
+// output coordinate, the same sequential-k fma order as the tiled contraction.  A matrix
+// element is loaded once and used for all RPB rows of the block.
+template <int XDT, int RPB>
+__global__ void k_project_rows(const void* x, int64_t n, int K, const float* __restrict__ m, int N, float* out) {
+  __shared__ float xs[RPB][TQ_MAX_DIM];
+  const int64_t row0 = (int64_t)blockIdx.x * RPB;
+#pragma unroll
+  for (int r = 0; r < RPB; ++r)
+    for (int k = threadIdx.x; k < K; k += blockDim.x) xs[r][k] = row0 + r < n ? load_elem<XDT>(x, (row0 + r) * K + k) : 0.f;
   __syncthreads();
-  for (int n = threadIdx.x; n < N; n += blockDim.x) {
-    float acc = 0.f;
+  for (int col = threadIdx.x; col < N; col += blockDim.x) {
+    float acc[RPB];
+#pragma unroll
+    for (int r = 0; r < RPB; ++r) acc[r] = 0.f;
     int k = 0;
-    for (; k + 32 <= K; k += 32) {               // 32 independent loads in flight, then the ordered fma chain
-      float mv[32];
+    for (; k + 16 <= K; k += 16) {               // 16 independent loads in flight, then the ordered fma chains
+      float mv[16];
 #pragma unroll
-      for (int u = 0; u < 32; ++u) mv[u] = __ldg(m + (int64_t)(k + u) * N + n);
+      for (int u = 0; u < 16; ++u) mv[u] = __ldg(m + (int64_t)(k + u) * N + col);
 #pragma unroll
-      for (int u = 0; u < 32; ++u) acc = fmaf(xs[k + u], mv[u], acc);
+      for (int u = 0; u < 16; ++u)
+#pragma unroll
+        for (int r = 0; r < RPB; ++r) acc[r] = fmaf(xs[r][k + u], mv[u], acc[r]);
     }
-    for (; k < K; ++k) acc = fmaf(xs[k], __ldg(m + (int64_t)k * N + n), acc);
-    out[row * N + n] = acc;
+    for (; k < K; ++k) {
+      const float mv = __ldg(m + (int64_t)k * N + col);
+#pragma unroll
+      for (int r = 0; r < RPB; ++r) acc[r] = fmaf(xs[r][k], mv, acc[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < RPB; ++r)
+      if (row0 + r < n) out[(row0 + r) * N + col] = acc[r];
   }
 }
 
@@ -976,9 +989,13 @@ int simt_dequantize(const TqDequantizeJob& job, cudaStream_t st) {
 
 int simt_project(const void* x, int x_dtype, int64_t n, int K, const float* m, int N, float* out, cudaStream_t st) {
   if (n == 0) return TQ_OK;
-  if (n <= 512) {          // few rows: a tile kernel would run on a handful of SMs
+  if (n <= 8192) {         // few rows: a 64-row tile kernel would run on a handful of SMs
     const int threads = N <= 128 ? 128 : 256;
-    TQ_DISPATCH_DT(x_dtype, k_project_rows<DT_><<<(unsigned)n, threads, 0, st>>>(x, K, m, N, out));
+    if (n <= 512) {
+      TQ_DISPATCH_DT(x_dtype, (k_project_rows<DT_, 1><<<(unsigned)n, threads, 0, st>>>(x, n, K, m, N, out)));
+    } else {
+      TQ_DISPATCH_DT(x_dtype, (k_project_rows<DT_, 4><<<(unsigned)((n + 3) / 4), threads, 0, st>>>(x, n, K, m, N, out)));
+    }
     return check_launch();
   }
   const int nj = nj_for(N);
