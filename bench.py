@@ -242,11 +242,15 @@ def run_side_workload(args, dev):
                    value=n * steps / t1, ms_per_step=1e3 * t1 / steps, dtype="f32",
                    config={"workload": "configs[4]: (1,16,16384,256) fp16, 3-bit TurboQuantCompressorV2, 64 queries/head"},
                    compress={"vectors/s": n * steps / t1, "GB/s": n * 1282 * steps / t1 / 1e9, "TFLOP/s": n * 393216 * steps / t1 / 1e12},
-                   scores={"keys/s": n * steps / t2, "GB/s": n * 1026 * steps / t2 / 1e9, "ms": 1e3 * t2 / steps},
+                   scores={"keys/s": n * steps / t2, "GB/s": n * 1026 * steps / t2 / 1e9, "ms": 1e3 * t2 / steps,
+                           "frac_of_hbm_peak": n * 1026 * steps / t2 / 1e9 / peak,
+                           "note": "tcgen05 kernel (k_umma_qjl_scores) plus its query projection and image kernels"},
                    roofline={"bound": "tensor", "achieved": n * 393216 * steps / t1 / 1e12,
                              "peak": float(peaks.get("bf16_tflops_sustained", 1400.0)), "unit": "TFLOP/s",
                              "frac": n * 393216 * steps / t1 / 1e12 / float(peaks.get("bf16_tflops_sustained", 1400.0)),
-                             "traffic": None, "note": "FP32 CUDA-core kernels: no tensor-core path for head_dim 256 yet"})
+                             "traffic": None, "note": "roofline of the compress kernel, which is FP32 CUDA-core code "
+                                                       "(three chained 256x256 contractions); the score kernel runs on "
+                                                       "tensor cores and is HBM-bound, see scores.frac_of_hbm_peak"})
     elif args.workload == "decode":
         # generation loop on the incremental cache: prefill 8192 tokens per layer, then one token per step
         from turboquant.cache import V3Cache
