@@ -510,3 +510,20 @@ def test_v2_scores_tensor_core_shapes(d, sq, sk, bh):
     assert rel_err(sc, sc_simt) <= 1e-5
     from turboquant import _native
     assert _native.lib().tq_last_device_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits,hq,hkv,sq,sk", [(4, 8, 2, 1, 1000), (2, 4, 4, 3, 129), (8, 16, 1, 1, 300), (3, 2, 2, 8, 77),
+                                                (6, 32, 8, 1, 2048), (4, 8, 2, 5, 500)])
+def test_packed_scores_shapes_and_widths(bits, hq, hkv, sq, sk):
+    """Logits and softmax from packed keys for several code widths, GQA group sizes, query counts and ragged key
+    counts, against the oracle composition (decompress + matmul)."""
+    keys = O.synthetic_kv((2, hkv, sk, 128), torch.float16, seed=53000 + bits + sk)
+    q = torch.randn(2, hq, sq, 128, generator=torch.Generator().manual_seed(bits * 10 + sq))
+    comp = tq.MSECompressor(128, bits, seed=77, device=DEV)
+    c = comp.compress(keys.to(DEV))
+    logits, probs = comp.attention_scores(q.to(DEV), c, scale=0.25, softmax=True)
+    rec = comp.decompress(c).cpu()
+    want = O.v3_scores(q, rec) * 0.25
+    assert logits.shape == (2, hq, sq, sk) and rel_err(logits, want) <= 1e-5
+    assert torch.allclose(probs.cpu(), torch.softmax(want, -1), rtol=2e-4, atol=1e-7)
