@@ -462,12 +462,13 @@ __global__ void k_project_rows(const void* x, int64_t n, int K, const float* __r
 #pragma unroll
     for (int r = 0; r < RPB; ++r) acc[r] = 0.f;
     int k = 0;
-    for (; k + 16 <= K; k += 16) {               // 16 independent loads in flight, then the ordered fma chains
-      float mv[16];
+    constexpr int kBatch = RPB == 1 ? 64 : 16;   // independent loads in flight before the ordered fma chains
+    for (; k + kBatch <= K; k += kBatch) {
+      float mv[kBatch];
 #pragma unroll
-      for (int u = 0; u < 16; ++u) mv[u] = __ldg(m + (int64_t)(k + u) * N + col);
+      for (int u = 0; u < kBatch; ++u) mv[u] = __ldg(m + (int64_t)(k + u) * N + col);
 #pragma unroll
-      for (int u = 0; u < 16; ++u)
+      for (int u = 0; u < kBatch; ++u)
 #pragma unroll
         for (int r = 0; r < RPB; ++r) acc[r] = fmaf(xs[r][k + u], mv[u], acc[r]);
     }
@@ -670,9 +671,20 @@ __global__ void __launch_bounds__(NT) k_softmax_finish(const float* __restrict__
   }
   __syncthreads();
   const float m = sh_m, inv = 1.f / sh_z;
-  const int64_t per = (Sk + gridDim.y - 1) / gridDim.y;
+  const int64_t per = ((Sk + gridDim.y - 1) / gridDim.y + 3) / 4 * 4;
   const int64_t lo = blockIdx.y * per, hi = min(lo + per, Sk);
-  for (int64_t s = lo + threadIdx.x; s < hi; s += NT) probs[row * Sk + s] = __expf(logits[row * Sk + s] - m) * inv;
+  const float* src = logits + row * Sk;
+  float* dst = probs + row * Sk;
+  if ((Sk & 3) == 0 && (((uintptr_t)src | (uintptr_t)dst) & 15u) == 0) {     // 16-byte rows: four logits per access
+    for (int64_t s = lo + 4 * (int64_t)threadIdx.x; s < hi; s += 4 * NT) {
+      const float4 l = *reinterpret_cast<const float4*>(src + s);
+      float4 p;
+      p.x = __expf(l.x - m) * inv; p.y = __expf(l.y - m) * inv; p.z = __expf(l.z - m) * inv; p.w = __expf(l.w - m) * inv;
+      *reinterpret_cast<float4*>(dst + s) = p;
+    }
+  } else {
+    for (int64_t s = lo + threadIdx.x; s < hi; s += NT) dst[s] = __expf(src[s] - m) * inv;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -1045,7 +1057,7 @@ int simt_score_packed(const TqScoreJob& job, cudaStream_t st) {
   }
   rc = check_launch();
   if (rc != TQ_OK || job.probs == nullptr) return rc;
-  int chunks = (int)((job.Sk + 16383) / 16384);
+  int chunks = (int)((job.Sk + 4095) / 4096);
   dim3 grid((unsigned)rows, (unsigned)chunks);
   k_softmax_finish<<<grid, NT, 0, st>>>(job.logits, stats, nblk, job.Sk, job.probs);
   return check_launch();
