@@ -233,7 +233,16 @@ typedef struct {
   void* idx_out;          /* [dev] or NULL                                                    */
   void* signs_out;        /* [dev] (N, M)                                                     */
   void* rnorm_out;        /* [dev] (N)                                                        */
+  void* workspace;        /* [dev] scratch for the tensor-core path, or NULL (FP32 kernels)   */
+  size_t workspace_bytes; /* >= tq_qjl_compress_workspace_bytes(N, D) to enable that path     */
 } TqQjlCompressJob;
+
+/* Scratch the tensor-core path of tq_qjl_compress needs for N vectors (operand images of the three
+ * matrices, two fp16 piece arrays of N x D, N norms); 0 when head_dim has no such path.  That path
+ * serves contiguous fp16 vectors with head_dim 128 or 256, normalize = 1, M = D, int8 signs, fp16
+ * norms and k_mse_out set; every other job, and any job without enough scratch, runs on the FP32
+ * kernels with identical semantics.                                                            */
+size_t tq_qjl_compress_workspace_bytes(int64_t n_vectors, int D);
 
 /* Replaces: TurboQuantCompressorV2.compress turboquant/compressors.py:83-120;
  * TurboQuantProd.quantize turboquant/turboquant.py:134-159.                    */

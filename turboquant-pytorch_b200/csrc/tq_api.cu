@@ -281,7 +281,9 @@ int tq_prepare_rotation_image(const float* m, int D, void* image, void* stream) 
 
 int tq_last_device_status(void) {
   const int a = tq::umma_device_status();
-  return a != 0 ? a : tq::umma_qjl_device_status();
+  if (a != 0) return a;
+  const int b = tq::umma_qjl_device_status();
+  return b != 0 ? b : tq::umma_v2_device_status();
 }
 
 int tq_quantize_rotated(const float* y, int64_t n, int D, int bits, const float* codebook, int idx_mode, void* out,
@@ -401,7 +403,13 @@ int tq_qjl_compress(const TqQjlCompressJob* job, void* stream) {
   if (job->x == nullptr || job->rotation_t == nullptr || job->rotation == nullptr || job->codebook == nullptr ||
       job->qjl_t == nullptr || job->signs_out == nullptr || job->rnorm_out == nullptr)
     return TQ_ENULL;
+  if (tq::umma_v2_compress_eligible(*job)) return tq::umma_v2_compress(*job, (cudaStream_t)stream);
   return tq::simt_qjl_compress(*job, (cudaStream_t)stream);
+}
+
+size_t tq_qjl_compress_workspace_bytes(int64_t n_vectors, int D) {
+  if (n_vectors <= 0) return 0;
+  return tq::umma_v2_compress_workspace(n_vectors, D);
 }
 
 size_t tq_qjl_scores_workspace_bytes(int64_t BH, int64_t Sq, int D) {

@@ -45,6 +45,12 @@ typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint3
                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 TensorMapEncodeFn tensor_map_encoder();
 
+// tensor-core MSE + QJL compress stage (tq_v2_umma.cu)
+size_t umma_v2_compress_workspace(int64_t n, int D);
+bool umma_v2_compress_eligible(const TqQjlCompressJob& job);
+int umma_v2_compress(const TqQjlCompressJob& job, cudaStream_t st);
+int umma_v2_device_status();
+
 // tensor-core asymmetric scores of the MSE+QJL representation (tq_qjl_umma.cu)
 bool umma_qjl_scores_eligible(const TqQjlScoreJob& job);
 size_t umma_qjl_scores_image_bytes(int64_t BH, int64_t Sq, int D);

@@ -57,7 +57,8 @@ class QjlCompressJob(C.Structure):
                 ("stride_b", C.c_int64), ("stride_h", C.c_int64), ("stride_s", C.c_int64),
                 ("rotation_t", C.c_void_p), ("rotation", C.c_void_p), ("codebook", C.c_void_p), ("qjl_t", C.c_void_p),
                 ("M", C.c_int32), ("signs_dtype", C.c_int32), ("rnorm_dtype", C.c_int32), ("idx_mode", C.c_int32),
-                ("k_mse_out", C.c_void_p), ("idx_out", C.c_void_p), ("signs_out", C.c_void_p), ("rnorm_out", C.c_void_p)]
+                ("k_mse_out", C.c_void_p), ("idx_out", C.c_void_p), ("signs_out", C.c_void_p), ("rnorm_out", C.c_void_p),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
 
 
 class QjlScoreJob(C.Structure):
@@ -101,6 +102,8 @@ def lib():
     L.tq_score_packed.argtypes = [C.POINTER(ScoreJob), vp]
     L.tq_score_packed_noalloc.argtypes = [C.POINTER(ScoreJob), vp]
     L.tq_qjl_compress.argtypes = [C.POINTER(QjlCompressJob), vp]
+    L.tq_qjl_compress_workspace_bytes.restype = sz
+    L.tq_qjl_compress_workspace_bytes.argtypes = [i64, i32]
     L.tq_qjl_scores_workspace_bytes.restype = sz
     L.tq_qjl_scores_workspace_bytes.argtypes = [i64, i64, i32]
     L.tq_qjl_scores.argtypes = [C.POINTER(QjlScoreJob), vp]

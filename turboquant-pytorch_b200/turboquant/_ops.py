@@ -163,12 +163,20 @@ def qjl_compress(x: torch.Tensor, pi: torch.Tensor, pi_t: torch.Tensor, codebook
         idx = torch.empty((n, D), dtype=torch.int64 if idx_mode == N.IDX_I64 else torch.uint8, device=dev)
     signs = torch.empty((n, M), dtype=torch.float32 if signs_fp32 else torch.int8, device=dev)
     rnorm = torch.empty((n,), dtype=torch.float32 if rnorm_fp32 else torch.float16, device=dev)
+    # scratch for the tensor-core path (fp16 vectors, head_dim 128 / 256, the V2 output formats); without it
+    # the library runs the FP32 kernels
+    ws, ws_bytes = None, 0
+    if x.dtype == torch.float16 and normalize and want_k_mse and idx_mode is None and not signs_fp32 and not rnorm_fp32:
+        ws_bytes = N.lib().tq_qjl_compress_workspace_bytes(n, D)
+        if ws_bytes:
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     job = N.QjlCompressJob(x=x.data_ptr(), x_dtype=N.dtype_code(x), D=D, bits=bits, normalize=int(normalize), B=B, H=H,
                            S=S, stride_b=sb, stride_h=sh, stride_s=ss, rotation_t=pi_t.data_ptr(),
                            rotation=pi.data_ptr(), codebook=codebook.data_ptr(), qjl_t=qjl_t.data_ptr(), M=M,
                            signs_dtype=int(signs_fp32), rnorm_dtype=N.F32 if rnorm_fp32 else N.F16,
                            idx_mode=idx_mode if idx_mode is not None else N.IDX_U8, k_mse_out=_ptr(k_mse),
-                           idx_out=_ptr(idx), signs_out=signs.data_ptr(), rnorm_out=rnorm.data_ptr())
+                           idx_out=_ptr(idx), signs_out=signs.data_ptr(), rnorm_out=rnorm.data_ptr(),
+                           workspace=_ptr(ws), workspace_bytes=ws_bytes)
     with torch.cuda.device(dev):
         N.check(N.lib().tq_qjl_compress(C.byref(job), N.stream_ptr(dev)), "tq_qjl_compress")
     return k_mse, idx, signs, rnorm
