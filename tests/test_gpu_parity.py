@@ -527,3 +527,39 @@ def test_packed_scores_shapes_and_widths(bits, hq, hkv, sq, sk):
     want = O.v3_scores(q, rec) * 0.25
     assert logits.shape == (2, hq, sq, sk) and rel_err(logits, want) <= 1e-5
     assert torch.allclose(probs.cpu(), torch.softmax(want, -1), rtol=2e-4, atol=1e-7)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("d,bits,shape", [(128, 3, (1, 2, 300, 128)), (256, 3, (2, 3, 77, 256)), (256, 5, (1, 1, 513, 256)),
+                                          (128, 2, (1, 4, 128, 128))])
+def test_v2_compress_tensor_core_against_fp32_kernels(d, bits, shape):
+    """MSE+QJL compress on the tensor-core path (fp16, head_dim 128/256) against the oracle and the FP32 kernels:
+    ragged tile counts, several widths of the MSE stage."""
+    import os
+    x = O.synthetic_kv(shape, torch.float16, seed=54000 + d + bits, outlier_channels=0)
+    comp = tq.TurboQuantCompressorV2(d, bits, seed=13, device=DEV)
+    c = comp.compress(x.to(DEV))
+    want = O.v2_compress(x, comp.Pi.cpu(), comp.centroids.cpu(), comp.S.cpu())
+    assert c["k_mse"].shape == x.shape and c["qjl_signs"].shape == x.shape and c["residual_norm"].shape == x.shape[:3]
+    def vectors_close(a, b):
+        """Per vector: within 2e-3 of the tensor's scale.  A rotated value that sits on a threshold may take the
+        neighbouring index on one path (about one coordinate in 1e5), which moves that vector's k_mse, its
+        residual norm and some of its signs; all other vectors agree."""
+        a, b = a.float().cpu(), b.float().cpu()
+        return (a - b).abs().amax(-1) <= 2e-3 * float(b.abs().max())
+
+    ok_vec = vectors_close(c["k_mse"], want["k_mse"])
+    assert ok_vec.float().mean() >= 0.99
+    assert rel_err(c["k_mse"], want["k_mse"]) <= 5e-2                 # a neighbouring index is a bounded error
+    assert (c["qjl_signs"].cpu() == want["qjl_signs"]).float().mean() >= 0.999
+    assert set(c["qjl_signs"].unique().tolist()) <= {-1, 1}
+    check_norms(c["residual_norm"][ok_vec.to(DEV)], want["residual_norm"].float()[ok_vec])
+    os.environ["TQ_FORCE_SIMT"] = "1"
+    try:
+        c2 = comp.compress(x.to(DEV))
+    finally:
+        del os.environ["TQ_FORCE_SIMT"]
+    assert vectors_close(c["k_mse"], c2["k_mse"]).float().mean() >= 0.99
+    assert (c["qjl_signs"] == c2["qjl_signs"]).float().mean() >= 0.999
+    from turboquant import _native
+    assert _native.lib().tq_last_device_status() == 0

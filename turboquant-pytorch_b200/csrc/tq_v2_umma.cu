@@ -14,8 +14,8 @@
 // (128 rows x 64 columns, 128-byte swizzle, one slot per k-chunk and piece) and bulk copies of
 // B chunks (128 output columns x 64 k, 16 KB, pre-swizzled image in global memory, L2-resident)
 // through a ring; warp 1: tcgen05.mma M=128 N=128 K=16 into one 128-column accumulator per
-// block of 128 output columns; warps 2..9: two epilogue warpgroups on alternate tiles, thread =
-// vector.  Every mbarrier wait is bounded; on expiry the CTA raises an abort flag, records a
+// block of 128 output columns; the other warps: per tile in flight (two) one epilogue warpgroup
+// per block of 128 columns, thread = vector.  Every mbarrier wait is bounded; on expiry the CTA raises an abort flag, records a
 // status word and leaves through the normal exit.
 
 #include <cuda.h>
@@ -36,7 +36,6 @@ namespace {
 constexpr int kRowsT = 128;                    // vectors per tile (MMA M)
 constexpr uint32_t kChunk = 128 * 128;         // 128 rows x 64 fp16 = 16 KB (an A chunk or a B chunk)
 constexpr int kNB = 4;                         // B ring stages
-constexpr int kThreadsV = 64 + 8 * 32;         // 320
 
 template <int D>
 struct VCfg {
@@ -44,8 +43,9 @@ struct VCfg {
   static constexpr int NBLK = D / 128;         // blocks of 128 output columns
   static constexpr uint32_t kOffA = 0;                                   // [piece 2][kc] chunks
   static constexpr uint32_t kOffB = kOffA + 2u * KC * kChunk;            // ring
-  static constexpr uint32_t kOffTab = kOffB + kNB * kChunk;              // 256 thresholds + 256 centroid piece pairs
-  static constexpr uint32_t kOffBar = kOffTab + 2048;
+  static constexpr uint32_t kOffTab = kOffB + kNB * kChunk;              // thresholds, centroid piece pairs, cell table, partial sums
+  static constexpr uint32_t kOffBar = kOffTab + 6144;
+  static constexpr int kThreads = 64 + 2 * NBLK * 128;                   // two tiles in flight, one warpgroup per 128 columns
   static constexpr uint32_t kUsedBytes = kOffBar + 256;
   static constexpr uint32_t kSmemBytes = kUsedBytes + 1024;
   static constexpr uint32_t kImageBytes = 2u * KC * NBLK * kChunk;       // [piece][kc][nb] chunks of one operand
@@ -105,7 +105,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 
 template <int D, int STAGE>
-__global__ void __launch_bounds__(kThreadsV, 1) k_umma_v2_stage(const __grid_constant__ V2Stage p) {
+__global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __grid_constant__ V2Stage p) {
   using C = VCfg<D>;
   constexpr int KC = C::KC, NBLK = C::NBLK;
   constexpr int PA = STAGE == 1 ? 1 : 2;       // pieces of A
@@ -124,6 +124,8 @@ __global__ void __launch_bounds__(kThreadsV, 1) k_umma_v2_stage(const __grid_con
   const uint32_t b_smem = base + C::kOffB;
   float* thr_s = reinterpret_cast<float*>(gbase + C::kOffTab);
   uint32_t* lut_s = reinterpret_cast<uint32_t*>(gbase + C::kOffTab + 1024);
+  uint8_t* cells_s = gbase + C::kOffTab + 2048;                        // 1028 bytes
+  float* part_s = reinterpret_cast<float*>(gbase + C::kOffTab + 4096); // [slot 2][row 128] partial sums of the upper block
   const uint32_t bar0 = base + C::kOffBar;
   const uint32_t bar_afull = bar0;                          // [KC] TMA -> MMA (all pieces of a k-chunk)
   const uint32_t bar_aempty = bar_afull + 8 * 4;            // [KC] MMA commit -> producer
@@ -143,7 +145,7 @@ __global__ void __launch_bounds__(kThreadsV, 1) k_umma_v2_stage(const __grid_con
   if (threadIdx.x == 0) {
     for (int i = 0; i < KC; ++i) { mbar_init(bar_afull + 8 * i, 1); mbar_init(bar_aempty + 8 * i, 1); }
     for (int i = 0; i < kNB; ++i) { mbar_init(bar_bfull + 8 * i, 1); mbar_init(bar_bempty + 8 * i, 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, 4); }
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, 4 * NBLK); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -155,6 +157,7 @@ __global__ void __launch_bounds__(kThreadsV, 1) k_umma_v2_stage(const __grid_con
       const __half h = __float2half_rn(c);
       const __half l = __float2half_rn(c - __half2float(h));
       lut_s[e] = (uint32_t)__half_as_ushort(h) | ((uint32_t)__half_as_ushort(l) << 16);
+      for (int w = e; w < 257; w += 256) reinterpret_cast<uint32_t*>(cells_s)[w] = __float_as_uint(__ldg(p.codebook + 528 + w));
     }
   }
   if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), C::kTmemCols);
@@ -257,45 +260,76 @@ __global__ void __launch_bounds__(kThreadsV, 1) k_umma_v2_stage(const __grid_con
       if (p.status != nullptr) atomicCAS(p.status, 0, (STAGE << 20) | (2 << 16) | (int)blockIdx.x);
     }
   } else {
-    // ------------------------------------------------------------ epilogue: two warpgroups on alternate tiles, thread = vector
+    // ------------------------------------------------------------ epilogue: per tile in flight one warpgroup per block
+    // of 128 output columns, thread = vector
     const int ew = warp - 2;
-    const int wg = ew >> 2;
+    const int wgi = ew >> 2;
+    const int slot = wgi / NBLK, blk = wgi % NBLK;
     const int quarter = warp & 3;                 // TMEM lanes this warp may touch: 32*quarter ..
     const int rloc = quarter * 32 + lane;
     bool ok = true;
-    for (int i = wg; i < n_local && ok; i += 2) {
+    // search shortcut of the codebook (stage 1): 1 = polynomial, 2 = cell table, 0 = binary search
+    int mode = 0;
+    float sc_s = 0.f, sc_c1 = 0.f, sc_c2 = 0.f, sc_c3 = 0.f;
+    if constexpr (STAGE == 1) {
+      mode = (int)__ldg(p.codebook + 512);
+      sc_s = __ldg(p.codebook + 513);
+      sc_c1 = __ldg(p.codebook + 514);
+      sc_c2 = __ldg(p.codebook + 515);
+      sc_c3 = __ldg(p.codebook + 516);
+    }
+    for (int i = slot; i < n_local && ok; i += 2) {
       const int64_t row = (int64_t)(t0 + i) * kRowsT + rloc;
       const bool valid = row < p.n;
-      ok = mbar_wait(bar_tfull + 8 * wg, (uint32_t)((i >> 1) & 1), abort_flag);
+      ok = mbar_wait(bar_tfull + 8 * slot, (uint32_t)((i >> 1) & 1), abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(wg * NBLK * 128);
+      const uint32_t tile_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(slot * NBLK * 128);
+      const uint32_t tacc = tile_acc + (uint32_t)(blk * 128);     // this warpgroup's block of columns
+      const int col0 = blk * 128;
       uint32_t v[16];
       if constexpr (STAGE == 1) {
-        float ssq = 0.f;
+        float ssq = 0.f;                         // the norm needs every column: both warpgroups sweep the whole row
 #pragma unroll 1
         for (int c = 0; c < D / 16; ++c) {
-          tmem_ld16(tacc + c * 16, v);
+          tmem_ld16(tile_acc + c * 16, v);
 #pragma unroll
           for (int e = 0; e < 16; ++e) ssq = fmaf(__uint_as_float(v[e]), __uint_as_float(v[e]), ssq);
         }
         const float norm = __fsqrt_rn(ssq);
         const float inv = __fdiv_rn(1.0f, norm + 1e-8f);
-        if (valid) p.norms[row] = norm;
+        if (valid && blk == 0) p.norms[row] = norm;
         const int bits = p.bits;
 #pragma unroll 1
-        for (int c = 0; c < D / 16; ++c) {
+        for (int c = 0; c < 8; ++c) {
           tmem_ld16(tacc + c * 16, v);
           uint32_t w[16];
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
             const float y = __uint_as_float(v[e]) * inv;
-            int lo = 0, hi = (1 << bits) - 1;
-            for (int step = 0; step < bits; ++step) {
-              const int mid = (lo + hi) >> 1;
-              if (y > thr_s[mid]) lo = mid + 1; else hi = mid;
+            int idx;
+            if (mode != 0) {
+              // candidate e0 with index in {e0, e0 + 1} (verified on the host for every y), then one exact compare
+              float t;
+              asm("fma.rn.sat.f32 %0, %1, %2, 0f3F000000;" : "=f"(t) : "f"(y), "f"(sc_s));
+              int e0;
+              if (mode == 1) {
+                float q = fmaf(sc_c3, t, sc_c2);
+                q = fmaf(q, t, sc_c1);
+                e0 = __float_as_int(fmaf(q, t, 8388608.0f)) & 0xFF;
+              } else {
+                e0 = cells_s[__float_as_int(fmaf(t, 1024.0f, 8388608.0f)) & 0x7FF];
+              }
+              idx = e0 + (y > thr_s[e0] ? 1 : 0);
+            } else {
+              int lo = 0, hi = (1 << bits) - 1;
+              for (int step = 0; step < bits; ++step) {
+                const int mid = (lo + hi) >> 1;
+                if (y > thr_s[mid]) lo = mid + 1; else hi = mid;
+              }
+              idx = lo;
             }
-            w[e] = lut_s[lo];
+            w[e] = lut_s[idx];
           }
           if (valid) {
             uint32_t ph[8], pl[8];
@@ -304,8 +338,8 @@ __global__ void __launch_bounds__(kThreadsV, 1) k_umma_v2_stage(const __grid_con
               ph[j] = __byte_perm(w[2 * j], w[2 * j + 1], 0x5410);
               pl[j] = __byte_perm(w[2 * j], w[2 * j + 1], 0x7632);
             }
-            uint4* dh = reinterpret_cast<uint4*>(p.p_hi + row * D + c * 16);
-            uint4* dl = reinterpret_cast<uint4*>(p.p_lo + row * D + c * 16);
+            uint4* dh = reinterpret_cast<uint4*>(p.p_hi + row * D + col0 + c * 16);
+            uint4* dl = reinterpret_cast<uint4*>(p.p_lo + row * D + col0 + c * 16);
             dh[0] = make_uint4(ph[0], ph[1], ph[2], ph[3]); dh[1] = make_uint4(ph[4], ph[5], ph[6], ph[7]);
             dl[0] = make_uint4(pl[0], pl[1], pl[2], pl[3]); dl[1] = make_uint4(pl[4], pl[5], pl[6], pl[7]);
           }
@@ -314,10 +348,10 @@ __global__ void __launch_bounds__(kThreadsV, 1) k_umma_v2_stage(const __grid_con
         const float nv = valid ? p.norms[row] : 0.f;
         float ssq = 0.f;
 #pragma unroll 1
-        for (int c = 0; c < D / 16; ++c) {
+        for (int c = 0; c < 8; ++c) {
           tmem_ld16(tacc + c * 16, v);
           if (valid) {
-            const uint4* xs = reinterpret_cast<const uint4*>(p.x + row * D + c * 16);
+            const uint4* xs = reinterpret_cast<const uint4*>(p.x + row * D + col0 + c * 16);
             const uint4 x0 = __ldg(xs), x1 = __ldg(xs + 1);
             const uint32_t xw[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
             uint32_t kq[8], rh[8], rl[8];
@@ -335,18 +369,25 @@ __global__ void __launch_bounds__(kThreadsV, 1) k_umma_v2_stage(const __grid_con
               const __half2 ll = __floats2half2_rn(r0 - __low2float(hh), r1 - __high2float(hh));
               rl[j] = *reinterpret_cast<const uint32_t*>(&ll);
             }
-            uint4* dk = reinterpret_cast<uint4*>(p.k_mse_out + row * D + c * 16);
-            uint4* dh = reinterpret_cast<uint4*>(p.p_hi + row * D + c * 16);
-            uint4* dl = reinterpret_cast<uint4*>(p.p_lo + row * D + c * 16);
+            uint4* dk = reinterpret_cast<uint4*>(p.k_mse_out + row * D + col0 + c * 16);
+            uint4* dh = reinterpret_cast<uint4*>(p.p_hi + row * D + col0 + c * 16);
+            uint4* dl = reinterpret_cast<uint4*>(p.p_lo + row * D + col0 + c * 16);
             dk[0] = make_uint4(kq[0], kq[1], kq[2], kq[3]); dk[1] = make_uint4(kq[4], kq[5], kq[6], kq[7]);
             dh[0] = make_uint4(rh[0], rh[1], rh[2], rh[3]); dh[1] = make_uint4(rh[4], rh[5], rh[6], rh[7]);
             dl[0] = make_uint4(rl[0], rl[1], rl[2], rl[3]); dl[1] = make_uint4(rl[4], rl[5], rl[6], rl[7]);
           }
         }
-        if (valid) p.rnorm_out[row] = __half_as_ushort(__float2half_rn(__fsqrt_rn(ssq)));
+        if constexpr (NBLK == 2) {
+          // the residual norm spans both blocks: the upper block's warpgroup hands its partial sum over
+          if (blk == 1) part_s[slot * 128 + rloc] = ssq;
+          asm volatile("bar.sync %0, 256;" ::"r"(1 + slot) : "memory");
+          if (blk == 0) ssq += part_s[slot * 128 + rloc];
+          asm volatile("bar.sync %0, 256;" ::"r"(1 + slot) : "memory");     // part_s is reused by the next tile
+        }
+        if (valid && blk == 0) p.rnorm_out[row] = __half_as_ushort(__float2half_rn(__fsqrt_rn(ssq)));
       } else {
 #pragma unroll 1
-        for (int c = 0; c < D / 16; ++c) {
+        for (int c = 0; c < 8; ++c) {
           tmem_ld16(tacc + c * 16, v);
           if (valid) {
             uint32_t sw[4];
@@ -360,13 +401,13 @@ __global__ void __launch_bounds__(kThreadsV, 1) k_umma_v2_stage(const __grid_con
               }
               sw[j] = x;
             }
-            *reinterpret_cast<uint4*>(p.signs_out + row * D + c * 16) = make_uint4(sw[0], sw[1], sw[2], sw[3]);
+            *reinterpret_cast<uint4*>(p.signs_out + row * D + col0 + c * 16) = make_uint4(sw[0], sw[1], sw[2], sw[3]);
           }
         }
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * wg);
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * slot);
     }
     if (!ok && lane == 0) {
       *abort_flag = 1;
@@ -403,7 +444,7 @@ int launch_stage(const V2Stage& p, int grid, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(k_umma_v2_stage<D, STAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)VCfg<D>::kSmemBytes);
   if (e != cudaSuccess) { note_cuda_error((int)e); return TQ_ELAUNCH; }
-  k_umma_v2_stage<D, STAGE><<<grid, kThreadsV, VCfg<D>::kSmemBytes, st>>>(p);
+  k_umma_v2_stage<D, STAGE><<<grid, VCfg<D>::kThreads, VCfg<D>::kSmemBytes, st>>>(p);
   return check_launch();
 }
 
