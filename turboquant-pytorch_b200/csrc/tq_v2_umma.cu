@@ -347,12 +347,15 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
       } else if constexpr (STAGE == 2) {
         const float nv = valid ? p.norms[row] : 0.f;
         float ssq = 0.f;
+        // the vector's own 16-coordinate pieces are fetched one step ahead of their use
+        const uint4* xrow = reinterpret_cast<const uint4*>(p.x + (valid ? row : 0) * D + col0);
+        uint4 nx0 = __ldg(xrow), nx1 = __ldg(xrow + 1);
 #pragma unroll 1
         for (int c = 0; c < 8; ++c) {
+          const uint4 x0 = nx0, x1 = nx1;
+          if (c + 1 < 8) { nx0 = __ldg(xrow + 2 * (c + 1)); nx1 = __ldg(xrow + 2 * (c + 1) + 1); }
           tmem_ld16(tacc + c * 16, v);
           if (valid) {
-            const uint4* xs = reinterpret_cast<const uint4*>(p.x + row * D + col0 + c * 16);
-            const uint4 x0 = __ldg(xs), x1 = __ldg(xs + 1);
             const uint32_t xw[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
             uint32_t kq[8], rh[8], rl[8];
 #pragma unroll
