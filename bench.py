@@ -248,9 +248,9 @@ def run_side_workload(args, dev):
                    roofline={"bound": "tensor", "achieved": n * 393216 * steps / t1 / 1e12,
                              "peak": float(peaks.get("bf16_tflops_sustained", 1400.0)), "unit": "TFLOP/s",
                              "frac": n * 393216 * steps / t1 / 1e12 / float(peaks.get("bf16_tflops_sustained", 1400.0)),
-                             "traffic": None, "note": "roofline of the compress kernel, which is FP32 CUDA-core code "
-                                                       "(three chained 256x256 contractions); the score kernel runs on "
-                                                       "tensor cores and is HBM-bound, see scores.frac_of_hbm_peak"})
+                             "traffic": None, "note": "compress = three tcgen05 contraction launches (k_umma_v2_stage); flops are "
+                                                       "the algorithmic 6 D^2 per vector, the hi/lo passes execute 2.7x "
+                                                       "that; the score kernel is HBM-bound, see scores.frac_of_hbm_peak"})
     elif args.workload == "decode":
         # generation loop on the incremental cache: prefill 8192 tokens per layer, then one token per step
         from turboquant.cache import V3Cache
