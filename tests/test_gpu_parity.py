@@ -563,3 +563,31 @@ def test_v2_compress_tensor_core_against_fp32_kernels(d, bits, shape):
     assert (c["qjl_signs"] == c2["qjl_signs"]).float().mean() >= 0.999
     from turboquant import _native
     assert _native.lib().tq_last_device_status() == 0
+
+
+@pytest.mark.gpu
+def test_cache_plan_replays_as_a_cuda_graph():
+    """compress + decompress of a whole cache captured once and replayed on new contents of the same buffers."""
+    from turboquant import batched
+    L = 3
+    codecs = [tq.TurboQuantV3(128, key_bits=4, value_bits=2, residual_window=0, layer_idx=l, n_layers=L, protected_layers=0,
+                              device=DEV) for l in range(L)]
+    keys = [O.synthetic_kv((1, 2, 384, 128), torch.float16, 900 + l).to(DEV) for l in range(L)]
+    vals = [O.synthetic_kv((1, 2, 384, 128), torch.float16, 950 + l).to(DEV) for l in range(L)]
+    plan = batched.CachePlan(codecs, keys, vals)
+    graph = plan.capture()
+    for t in keys + vals:                      # new contents, same storage
+        t.mul_(-0.5)
+    for ck, cv in plan.compressed:             # poison the outputs: the replay must rewrite them
+        ck["compressed"]["idx_bytes"].fill_(255)
+        cv["compressed"]["vec_norms"].zero_()
+    for rk, rv in plan.reconstructed:
+        rk.zero_(); rv.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    for l in range(L):
+        ck, cv = codecs[l].compress_kv(keys[l], vals[l])
+        assert torch.equal(plan.compressed[l][0]["compressed"]["idx_bytes"], ck["compressed"]["idx_bytes"])
+        assert torch.equal(plan.compressed[l][1]["compressed"]["vec_norms"], cv["compressed"]["vec_norms"])
+        rk, rv = codecs[l].decompress_kv(ck, cv)
+        assert torch.equal(plan.reconstructed[l][0], rk) and torch.equal(plan.reconstructed[l][1], rv)

@@ -12,6 +12,7 @@ int last_cuda_error();
 void note_cuda_error(int e);
 long long launch_count();
 int check_launch();   // cudaGetLastError -> TQ_OK / TQ_ELAUNCH, counts successful launches
+bool force_simt();    // TQ_FORCE_SIMT=1 in the environment: route everything to the FP32 kernels (second opinion in tests)
 
 // FP32 CUDA-core path (tq_simt.cu)
 int simt_quantize_rotated(const float* y, int64_t n, int D, int bits, const float* cb, int mode, void* out,

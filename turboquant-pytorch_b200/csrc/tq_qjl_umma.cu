@@ -377,11 +377,6 @@ __global__ void __launch_bounds__(kThreadsQ, 1) k_umma_qjl_scores(const __grid_c
   }
 }
 
-bool force_simt() {
-  const char* e = getenv("TQ_FORCE_SIMT");
-  return e != nullptr && e[0] == '1';
-}
-
 template <int D>
 int launch(const TqQjlScoreJob& job, const float* qf, const float* qproj, uint8_t* images, cudaStream_t st) {
   TensorMapEncodeFn enc = tensor_map_encoder();

@@ -77,7 +77,9 @@ struct UmmaQuantBatch {
   int32_t n_jobs;
   int32_t total_tiles;
   int32_t* status;           // device status word (may be null)
-  int32_t ablate;            // timing experiments only (TQ_ABLATE): 1 skip stores, 2 skip index math, 4 skip MMA
+  int32_t ablate;            // timing experiments only (TQ_ABLATE): 1 skip stores, 2 skip the epilogue, 4 skip MMA,
+                             // 16 no lane look-up, 32 half loads, 64 no loads, 128 arrive instead of commit,
+                             // 256 / 512 skip the quantise / norm sweep, 8192 MMAs as two N = 64 halves
   int32_t pad_[3];
   UmmaQuantJob jobs[kMaxJobs];
 };
@@ -1060,12 +1062,12 @@ int ablate_flags() {
   return e != nullptr ? atoi(e) : 0;
 }
 
+}  // namespace
+
 bool force_simt() {
   const char* e = getenv("TQ_FORCE_SIMT");
   return e != nullptr && e[0] == '1';
 }
-
-}  // namespace
 
 TensorMapEncodeFn tensor_map_encoder() {
   static std::atomic<void*> cached{nullptr};

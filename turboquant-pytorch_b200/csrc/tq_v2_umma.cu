@@ -425,11 +425,6 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
   }
 }
 
-bool force_simt() {
-  const char* e = getenv("TQ_FORCE_SIMT");
-  return e != nullptr && e[0] == '1';
-}
-
 int encode_rows(TensorMapEncodeFn enc, CUtensorMap* map, const void* ptr, int64_t n, int D) {
   cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)n};
   cuuint64_t strides[1] = {(cuuint64_t)D * 2};

@@ -105,6 +105,31 @@ class CachePlan:
         return self.reconstructed
 
     @torch.no_grad()
+    def capture(self, decompress: bool = True) -> "torch.cuda.CUDAGraph":
+        """compress() (and decompress()) recorded into a CUDA graph for replay with `graph.replay()`.
+
+        The plan's buffers and job arrays are static, and from its second call on the library only issues the
+        kernel launch for an unchanged job array, so the calls can be stream-captured; one eager pass runs first.
+        A plan with a residual window copies the window tokens inside the graph as well."""
+        has_window = any(ck["compressed"] is not None and ck["fp16"].shape[2] > 0 for ck, _ in self.compressed)
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):             # eager pass: the library builds and keeps its launch descriptions
+            self.compress()
+            if decompress:
+                self.decompress()
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.compress()
+            if decompress:
+                if has_window:
+                    self.refresh_window()
+                self.decompress()
+        return graph
+
+    @torch.no_grad()
     def refresh_window(self):
         for (ck, cv), outs in zip(self.compressed, self.reconstructed):
             if ck["compressed"] is None:
