@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is importable:
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <checkout of tonbistudio/turboquant-pytorch>
 
 The script imports the reference package `turboquant` (CPU), feeds it seeded
 inputs and stores inputs and outputs as .npz files next to this script.  The
@@ -46,7 +46,7 @@ def save(name: str, **arrays):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (the directory holding turboquant/)")
     ap.add_argument("--only", nargs="*", default=None, help="rewrite only these fixture files")
     args = ap.parse_args()
     global ONLY
