@@ -591,3 +591,27 @@ def test_cache_plan_replays_as_a_cuda_graph():
         assert torch.equal(plan.compressed[l][1]["compressed"]["vec_norms"], cv["compressed"]["vec_norms"])
         rk, rv = codecs[l].decompress_kv(ck, cv)
         assert torch.equal(plan.reconstructed[l][0], rk) and torch.equal(plan.reconstructed[l][1], rv)
+
+
+@pytest.mark.gpu
+def test_v2_tensor_core_edge_shapes():
+    """One vector, one key, a zero vector: the tensor-core V2 kernels against the oracle."""
+    for d in (128, 256):
+        comp = tq.TurboQuantCompressorV2(d, 3, seed=3, device=DEV)
+        x = O.synthetic_kv((1, 1, 3, d), torch.float16, seed=55000 + d, outlier_channels=0)
+        x[0, 0, 1] = 0                                  # zero vector: norm 0, every sign +1
+        for s in (1, 3):
+            xs = x[:, :, :s].contiguous()
+            c = comp.compress(xs.to(DEV))
+            want = O.v2_compress(xs, comp.Pi.cpu(), comp.centroids.cpu(), comp.S.cpu())
+            assert rel_err(c["k_mse"], want["k_mse"]) <= 2e-3
+            assert (c["qjl_signs"].cpu() == want["qjl_signs"]).float().mean() >= 0.99
+            check_norms(c["residual_norm"], want["residual_norm"].float())
+            if s == 3:
+                assert bool((c["qjl_signs"][0, 0, 1] == 1).all()) and float(c["k_mse"][0, 0, 1].abs().max()) == 0.0
+            q = torch.randn(1, 1, 2, d, generator=torch.Generator().manual_seed(s))
+            sc = comp.asymmetric_attention_scores(q.to(DEV), c)
+            ref = O.v2_scores(q, {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in c.items()}, comp.S.cpu())
+            assert sc.shape == (1, 1, 2, s) and rel_err(sc, ref) <= 1e-5
+    from turboquant import _native
+    assert _native.lib().tq_last_device_status() == 0
