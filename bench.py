@@ -57,7 +57,7 @@ def synthetic_layer(device, seed: int, dtype=torch.float16):
 
 
 class ClockSampler:
-    """Polls NVML (read only) for SM clock and throttle reasons while the timed region runs."""
+    """Polls NVML (read only) for SM clock and throttle reasons while the measured regions run."""
 
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
@@ -407,11 +407,14 @@ def main():
     e2e_step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e1.record()
-    barrier()
+    with ClockSampler(local_rank) as clocks_e2e:       # the second measured region; samples are pooled below
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+    clocks.samples += clocks_e2e.samples
+    clocks.reasons |= clocks_e2e.reasons
     t_e2e = torch.tensor([e0.elapsed_time(e1) * 1e-3], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
