@@ -615,3 +615,17 @@ def test_v2_tensor_core_edge_shapes():
             assert sc.shape == (1, 1, 2, s) and rel_err(sc, ref) <= 1e-5
     from turboquant import _native
     assert _native.lib().tq_last_device_status() == 0
+
+
+@pytest.mark.gpu
+def test_v2_compress_other_layouts_use_the_fp32_kernels():
+    """Inputs the tensor-core path does not take (a strided view, bf16 and fp32 vectors) give the same results
+    through the FP32 kernels."""
+    comp = tq.TurboQuantCompressorV2(128, 3, seed=17, device=DEV)
+    base = O.synthetic_kv((1, 2, 96, 128), torch.float16, seed=56000, outlier_channels=0)
+    for x in (base[:, :, ::2], base.to(torch.bfloat16), base.float()):
+        c = comp.compress(x.to(DEV) if x.is_contiguous() else base.to(DEV)[:, :, ::2])
+        want = O.v2_compress(x, comp.Pi.cpu(), comp.centroids.cpu(), comp.S.cpu())
+        assert c["k_mse"].shape == x.shape and rel_err(c["k_mse"], want["k_mse"]) <= 2e-3
+        assert (c["qjl_signs"].cpu() == want["qjl_signs"]).float().mean() >= 0.999
+        check_norms(c["residual_norm"], want["residual_norm"].float())
