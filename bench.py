@@ -1,21 +1,25 @@
 """Benchmark of the KV-cache compression hot path: quantize+pack then unpack+dequantize.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload ...]
 
-A step is one pass over a whole synthetic KV cache of the Qwen2.5-3B shape
-(36 layers x 2 KV heads x 8192 tokens x head_dim 128, fp16, 4 of 128 channels
-per head scaled x10): every layer's keys are quantised to 4 bits and values to
-2 bits (TurboQuantV3, residual_window=0, protected_layers=0), then every layer
-is dequantised back into fp16 tensors.  With N > 1 (torchrun, one rank per GPU)
-each rank processes its own cache of that size -- the (layer, KV head) units of
-an N-times larger batch -- with no collective on the data path (weak scaling).
+Default workload (`kv`): a whole synthetic KV cache of the Llama-3-8B shape -- 32 layers x
+8 KV heads x head_dim 128, batch 8, 32768 tokens, bf16, 4 of 128 channels per head scaled
+x10 -- through TurboQuantV3 with 6-bit keys, 4-bit values, the last 128 tokens kept in
+bf16 and the first/last 4 layers at 8 bits.  A step quantises + packs every layer's K and
+V, then dequantises every layer back into bf16 tensors (window tokens copied in), one
+library call per phase.  With N > 1 (torchrun, one rank per GPU) the 256 (layer, KV head)
+units of that ONE cache are split over the ranks in contiguous blocks, with no collective
+on the data path (strong scaling).  `--workload qwen` is the Qwen2.5-3B-shaped cache
+(36 layers x 2 KV heads, batch 1, 8192 tokens, fp16, K4/V2, no window).
 
-One JSON line is printed by rank 0.
+One JSON line is printed by rank 0.  The other workloads measure further rows of the path
+on one GPU (see run_side_workload).
 """
 
 from __future__ import annotations
 
 import argparse
+import importlib.util
 import json
 import os
 import statistics
@@ -28,32 +32,72 @@ sys.path.insert(0, os.path.join(ROOT, "turboquant-pytorch_b200"))
 
 import torch  # noqa: E402
 
-LAYERS, KV_HEADS, SEQ, HEAD_DIM = 36, 2, 8192, 128
-KEY_BITS, VALUE_BITS = 4, 2
+HEAD_DIM = 128
 METRIC = "KV vectors/s quantize+dequantize"
-WORKLOAD = ("configs[1]: Qwen2.5-3B-shaped KV cache, 36 layers x 2 KV heads x seq 8192 x head_dim 128, batch 1, fp16, "
-            "N(0,1) with 4/128 outlier channels x10, TurboQuantV3 K4/V2, residual_window=0, protected_layers=0")
+
+CACHES = {
+    "kv": dict(layers=32, kv_heads=8, batch=8, seq=32768, dtype=torch.bfloat16, key_bits=6, value_bits=4,
+               window=128, protected=4, seed=30000,
+               name="configs[2]: Llama-3-8B-shaped KV cache, 32 layers x 8 KV heads x head_dim 128, batch 8, seq 32768, "
+                    "bf16, N(0,1) with 4/128 outlier channels x10, TurboQuantV3 K6/V4, residual_window=128, "
+                    "protected_layers=4 (first/last 4 layers at 8 bits)"),
+    "qwen": dict(layers=36, kv_heads=2, batch=1, seq=8192, dtype=torch.float16, key_bits=4, value_bits=2,
+                 window=0, protected=0, seed=20000,
+                 name="configs[1]: Qwen2.5-3B-shaped KV cache, 36 layers x 2 KV heads x seq 8192 x head_dim 128, batch 1, "
+                      "fp16, N(0,1) with 4/128 outlier channels x10, TurboQuantV3 K4/V2, residual_window=0, "
+                      "protected_layers=0"),
+}
+
+# dram__bytes_read.sum + dram__bytes_write.sum per 128-vector tile of the dominant kernel, from ncu captures of a
+# smaller case of the same launch (the summaries name the commands); traffic grows in proportion to the tiles.
+NCU_DRAM_BYTES_PER_VECTOR = {}
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per full 72-job launch, from the ncu captures summarised in
-# profiles/ (18 layers captured, doubled: traffic grows in proportion to the vectors processed)
-NCU_DRAM_BYTES_PER_LAUNCH = {"quantize": 336.7e6, "dequantize": 246.2e6}
+def packed_row_bytes(bits: int) -> int:
+    ipb = 8 // bits
+    return (HEAD_DIM + ipb - 1) // ipb
 
 
 def algorithmic_bytes_per_vector(bits: int, elem_bytes: int = 2) -> int:
     """D*sizeof(elem) + packed row + fp16 norm, for quantise and for dequantise to the cache dtype."""
-    ipb = 8 // bits
-    return HEAD_DIM * elem_bytes + (HEAD_DIM + ipb - 1) // ipb + 2
+    return HEAD_DIM * elem_bytes + packed_row_bytes(bits) + 2
 
 
-def synthetic_layer(device, seed: int, dtype=torch.float16):
+def layer_bits(cfg, layer: int):
+    """(key_bits, value_bits) of a layer: protected layers use 8 bits for both (compressors_v3.py:157-164)."""
+    p = cfg["protected"]
+    if layer < p or layer >= cfg["layers"] - p:
+        return 8, 8
+    return cfg["key_bits"], cfg["value_bits"]
+
+
+def synthetic_layer(cfg, layer: int, kv: int, heads, device):
+    """One layer's K (kv=0) or V (kv=1) for the KV heads `heads` (a range), generated on the device.
+
+    The whole layer is drawn from one seeded generator and the rank's heads are sliced out, so the data of a
+    (layer, head) unit does not depend on how the cache is split over GPUs."""
+    B, H, S = cfg["batch"], cfg["kv_heads"], cfg["seq"]
+    seed = cfg["seed"] + 5000 * kv + layer
     g = torch.Generator(device=device).manual_seed(seed)
-    x = torch.randn(1, KV_HEADS, SEQ, HEAD_DIM, generator=g, device=device, dtype=torch.float32)
+    x = torch.randn(B, H, S, HEAD_DIM, generator=g, device=device, dtype=torch.float32)
     gc = torch.Generator(device="cpu").manual_seed(seed)
-    for h in range(KV_HEADS):
+    for h in range(H):
         ch = torch.randperm(HEAD_DIM, generator=gc)[:4].to(device)
         x[:, h, :, ch] *= 10.0
-    return x.to(dtype)
+    return x[:, heads.start:heads.stop].to(cfg["dtype"]).contiguous()
+
+
+def rank_layers(cfg, rank: int, world: int):
+    """[(layer, range of KV heads)] owned by `rank`: contiguous blocks of the layer-major (layer, head) units."""
+    from turboquant import batched
+    units = batched.shard_units(cfg["layers"], cfg["kv_heads"], rank, world)
+    out = []
+    for layer, head in units:
+        if out and out[-1][0] == layer:
+            out[-1] = (layer, range(out[-1][1].start, head + 1))
+        else:
+            out.append((layer, range(head, head + 1)))
+    return out
 
 
 class ClockSampler:
@@ -88,6 +132,7 @@ class ClockSampler:
             time.sleep(0.0005)
 
     def __enter__(self):
+        self._stop.clear()
         if self._nv is not None:
             self._thread = threading.Thread(target=self._run, daemon=True)
             self._thread.start()
@@ -103,51 +148,100 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def cpu_reference_pass(n_layers: int, threads: int):
-    """Oracle port of the reference's CPU path on `n_layers` layers; returns (vectors, seconds)."""
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import tq_oracle as O
-    torch.set_num_threads(threads)
-    cache = {}
-    vectors, seconds = 0, 0.0
-    for layer in range(n_layers):
-        codec = O.V3Oracle(HEAD_DIM, key_bits=KEY_BITS, value_bits=VALUE_BITS, residual_window=0, layer_idx=layer,
-                           n_layers=LAYERS, protected_layers=0, codebook_cache=cache)
-        keys = O.synthetic_kv((1, KV_HEADS, SEQ, HEAD_DIM), torch.float16, 20000 + layer)
-        vals = O.synthetic_kv((1, KV_HEADS, SEQ, HEAD_DIM), torch.float16, 25000 + layer)
+# ----------------------------------------------------------------------------- CPU arm
+def load_reference():
+    """The unmodified reference package when it was installed under baseline/_ref (pure Python, CPU torch),
+    under the module name turboquant_reference; None when it is absent."""
+    init = os.path.join(ROOT, "baseline", "_ref", "turboquant", "__init__.py")
+    if not os.path.exists(init):
+        return None
+    name = "turboquant_reference"
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(name, init, submodule_search_locations=[os.path.dirname(init)])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+class CpuSample:
+    """A bounded sample of the cache workload for the host cores: for each sampled layer, batch 0 / KV head 0,
+    `chunks` calls of TurboQuantV3.compress_kv + decompress_kv on (1, 1, chunk_tokens, 128) tensors.
+
+    Layers are sampled in the workload's own proportion of protected (8-bit) and ordinary layers.  The
+    reference materialises an (N, D, 2^bits) tensor per call (compressors_v3.py:60), which bounds the chunk."""
+
+    def __init__(self, cfg, threads: int, chunk_tokens: int = 8192, chunks: int = 1):
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import tq_oracle as O
+        torch.set_num_threads(threads)
+        self.cfg, self.chunk_tokens, self.chunks = cfg, chunk_tokens, chunks
+        ref = load_reference()
+        self.kind = "reference" if ref is not None else "port"
+        L, p = cfg["layers"], cfg["protected"]
+        if p > 0:
+            mid = L // 2
+            self.layers = [0] + [mid + i for i in range(max(1, round((L - 2 * p) / (2 * p))))]
+        else:
+            self.layers = [0, L // 2]
+        cache = {}
+        self.codecs, self.data = [], []
+        for layer in self.layers:
+            kw = dict(key_bits=cfg["key_bits"], value_bits=cfg["value_bits"], residual_window=cfg["window"],
+                      layer_idx=layer, n_layers=L, protected_layers=p)
+            if ref is not None:
+                codec = ref.TurboQuantV3(HEAD_DIM, device="cpu", **kw)
+            else:
+                codec = O.V3Oracle(HEAD_DIM, codebook_cache=cache, **kw)
+            self.codecs.append(codec)
+            shape = (1, 1, chunk_tokens, HEAD_DIM)
+            self.data.append([(O.synthetic_kv(shape, cfg["dtype"], cfg["seed"] + layer + 100 * c),
+                               O.synthetic_kv(shape, cfg["dtype"], cfg["seed"] + 5000 + layer + 100 * c))
+                              for c in range(chunks)])
+        self.vectors_per_pass = 2 * len(self.layers) * chunks * max(chunk_tokens - cfg["window"], 0)
+
+    def run(self):
+        """One pass over the sample; returns seconds."""
         t0 = time.perf_counter()
-        ck, cv = codec.compress_kv(keys, vals)
-        codec.decompress_kv(ck, cv)
-        seconds += time.perf_counter() - t0
-        vectors += 2 * KV_HEADS * SEQ
-    return vectors, seconds
+        for codec, chunks in zip(self.codecs, self.data):
+            for keys, vals in chunks:
+                ck, cv = codec.compress_kv(keys, vals)
+                codec.decompress_kv(ck, cv)
+        return time.perf_counter() - t0
+
+    def describe(self):
+        bits = [layer_bits(self.cfg, l) for l in self.layers]
+        return (f"layers {self.layers} (K/V bits {bits}), batch 0, KV head 0, {self.chunks} x {self.chunk_tokens} tokens each: "
+                f"TurboQuantV3.compress_kv + decompress_kv per chunk, {self.vectors_per_pass} quantised vectors per pass")
 
 
 def run_reference(args, rank: int):
+    """The reference's own CPU implementation of the path on the box's host cores (rank 0 only)."""
     if rank != 0:
         return
+    cfg = CACHES[args.workload if args.workload in CACHES else "kv"]
     threads = os.cpu_count() or 1
-    sample_layers = 4
-    for _ in range(args.warmup):
-        cpu_reference_pass(1, threads)
-    vec, sec = 0, 0.0
-    for _ in range(args.steps):
-        v, s = cpu_reference_pass(sample_layers, threads)
-        vec += v
-        sec += s
-    value = vec / sec
-    sample = f"{sample_layers} of {LAYERS} layers per step (K4 + V2, compress_kv + decompress_kv), {args.steps} steps"
+    sample = CpuSample(cfg, threads, chunk_tokens=8192 if cfg["seq"] >= 8192 else cfg["seq"])
+    for _ in range(min(args.warmup, 1)):
+        sample.run()
+    sec = sum(sample.run() for _ in range(args.steps))
+    value = sample.vectors_per_pass * args.steps / sec
+    what = ("the unmodified reference package (baseline/_ref), device='cpu'" if sample.kind == "reference" else
+            "CPU restatement of the reference (oracle/tq_oracle.py), torch CPU ops")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "vectors/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sec / max(args.steps, 1),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "arm": "CPU restatement of the reference (oracle/tq_oracle.py), torch CPU ops"},
-        "cpu_baseline": {"value": value, "unit": "vectors/s", "cores": threads, "kind": "port", "sample": sample},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": cfg["name"], "arm": what},
+        "cpu_baseline": {"value": value, "unit": "vectors/s", "cores": threads, "kind": sample.kind,
+                         "sample": sample.describe() + f"; {args.steps} passes"},
         "e2e": {"value": value, "unit": "vectors/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
 
 
+# ----------------------------------------------------------------------------- helpers
 def _time_steps(fn, steps, warmup, flush):
     """CUDA-event time of `steps` calls of fn (seconds), L2 flushed before each, flush outside the intervals."""
     for _ in range(warmup):
@@ -168,6 +262,7 @@ def directional_ceilings(flush):
     256 MiB flush buffer: a write-dominated kernel cannot reach the copy figure the roofline is quoted against."""
     n = flush.numel()
     half = n // 2
+
     def best(fn, reps=5):
         for _ in range(2):
             fn()
@@ -184,29 +279,125 @@ def directional_ceilings(flush):
     return {"read_only": n / tr / 1e9, "write_only": n / tw / 1e9, "copy": 2 * half / tc / 1e9}
 
 
+def load_peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        return {}
+
+
+def refuse_profiling_switches(lib):
+    """The timed library must be the normal build with no path-changing switch set."""
+    for var in ("TQ_ABLATE", "TQ_FORCE_SIMT"):
+        if os.environ.get(var):
+            raise SystemExit(f"bench.py: {var} is set; unset it (it changes or skips the kernels that are timed)")
+    if lib.tq_ablation_build():
+        raise SystemExit("bench.py: the loaded library is a -DTQ_ABLATION profiling build; rebuild with build.py")
+
+
+# ----------------------------------------------------------------------------- parity of the timed buffers
+def parity_block(cfg, layers, keys, vals, plan, tokens=4096, max_units=4):
+    """Check a fixed sub-slab of the buffers the timed steps produced against the CPU oracle.
+
+    Units: batch 0, the first `tokens` tokens of up to `max_units` (layer, KV head) pairs of this rank, chosen to
+    include a protected (8-bit) layer when the rank has one.  Index agreement with every mismatch attributed
+    to a decision boundary (neighbouring index, oracle-rotated value within 1e-6 of the boundary), fp16 norms
+    within 1 ulp, and the reconstruction against the oracle's decompression of the GPU's own packed bytes,
+    element-wise in units in the last place of the cache dtype."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import numpy as np
+    import tq_oracle as O
+    n_l = len(layers)
+    picks = sorted({0, n_l // 2, n_l - 1})
+    units = []
+    for li in picks:
+        nh = len(layers[li][1])
+        for hi in sorted({0, nh - 1}):
+            units.append((li, hi))
+    # keep one unit per picked layer first, then fill up
+    first = [u for u in units if u[1] == 0]
+    units = (first + [u for u in units if u not in first])[:max_units]
+    tok = min(tokens, cfg["seq"] - cfg["window"])
+    out = {"units": [], "vectors": 0, "index_mismatches": 0, "unattributed_mismatches": 0, "norm_ulp_gt1": 0,
+           "recon_max_rel_err": 0.0, "recon_frac_within_1ulp": 1.0, "recon_max_ulp": 0}
+    coords = 0
+    within = 0
+    elems = 0
+    cache = {}
+    for li, hi in units:
+        layer, heads = layers[li]
+        head = heads.start + hi
+        kb, vb = layer_bits(cfg, layer)
+        ref = O.V3Oracle(HEAD_DIM, key_bits=cfg["key_bits"], value_bits=cfg["value_bits"], residual_window=0,
+                         layer_idx=layer, n_layers=cfg["layers"], protected_layers=cfg["protected"],
+                         codebook_cache=cache)
+        ck, cv = plan.compressed[li]
+        rk, rv = plan.reconstructed[li]
+        out["units"].append({"layer": layer, "kv_head": head, "key_bits": kb, "value_bits": vb})
+        for x_dev, comp, rec, pi, cent, bits in ((keys[li], ck, rk, ref.k_pi, ref.k_cent, kb),
+                                                 (vals[li], cv, rv, ref.v_pi, ref.v_cent, vb)):
+            x = x_dev[0, hi, :tok].cpu()
+            idx_gpu = comp["compressed"]["idx_bytes"][0, hi, :tok].cpu().numpy()
+            norms_gpu = comp["compressed"]["vec_norms"][0, hi, :tok].cpu()
+            _flat, norms, rot = O.rotate_unit(x.reshape(1, 1, tok, HEAD_DIM), pi)
+            want = O.nearest_centroid(rot, cent).numpy()
+            got = O.unpack_indices(idx_gpu.reshape(tok, -1), bits, HEAD_DIM)
+            bnd = ((cent[:-1] + cent[1:]) / 2).numpy()
+            bad = np.argwhere(got != want)
+            out["index_mismatches"] += int(len(bad))
+            for r, c in bad:
+                y = float(rot[r, c])
+                if abs(int(got[r, c]) - int(want[r, c])) != 1 or np.min(np.abs(bnd - y)) >= 1e-6:
+                    out["unattributed_mismatches"] += 1
+            coords += want.size
+            g16 = norms_gpu.view(torch.int16).numpy().astype(np.int32)
+            w16 = norms.to(torch.float16).view(torch.int16).numpy().astype(np.int32).reshape(-1)
+            out["norm_ulp_gt1"] += int((np.abs(g16 - w16) > 1).sum())
+            # reconstruction: the oracle decompresses the bytes the GPU packed
+            comp_cpu = {"idx_bytes": torch.from_numpy(idx_gpu.reshape(1, 1, tok, -1).copy()),
+                        "vec_norms": norms_gpu.reshape(1, 1, tok), "shape": (1, 1, tok, HEAD_DIM), "idx_pad": 0}
+            want_rec = O.mse_decompress(comp_cpu, pi, cent, bits).reshape(tok, HEAD_DIM)
+            got_rec = rec[0, hi, :tok].cpu()
+            w_c = want_rec.to(got_rec.dtype)
+            err = (got_rec.float() - want_rec).abs()
+            scale = want_rec.abs().amax(dim=-1, keepdim=True).clamp_min(1e-30)
+            # before the final rounding to the cache dtype: take half a unit in the last place of each element off
+            half_ulp = (2.0 ** -8 if got_rec.dtype == torch.bfloat16 else 2.0 ** -11) * want_rec.abs()
+            out["recon_max_rel_err"] = max(out["recon_max_rel_err"], float(((err - half_ulp).clamp_min(0) / scale).max()))
+            key = lambda t: torch.where(t.view(torch.int16).int() < 0, -(t.view(torch.int16).int() & 0x7FFF),
+                                        t.view(torch.int16).int())     # sign-magnitude -> ordered integers
+            ulp = (key(got_rec) - key(w_c)).abs()
+            within += int((ulp <= 1).sum())
+            elems += ulp.numel()
+            out["recon_max_ulp"] = max(out["recon_max_ulp"], int(ulp.max()))
+            out["vectors"] += tok
+    out["index_agreement"] = 1.0 - out["index_mismatches"] / max(coords, 1)
+    out["recon_frac_within_1ulp"] = within / max(elems, 1)
+    out["tolerance"] = ("indices: every mismatch a neighbouring index whose oracle-rotated value is within 1e-6 of the "
+                        "boundary, agreement >= 99.99 %; norms: fp16 within 1 ulp; reconstruction: |error| <= 2e-3 of the "
+                        "vector's largest value plus the final rounding of the cache dtype (half a unit in the last place)")
+    out["ok"] = bool(out["unattributed_mismatches"] == 0 and out["index_agreement"] >= 0.9999 and
+                     out["norm_ulp_gt1"] == 0 and out["recon_max_rel_err"] <= 2e-3)
+    return out
+
+
+# ----------------------------------------------------------------------------- side workloads
 def run_side_workload(args, dev):
     """Other rows of the path, measured with the same hygiene; one JSON line each.
 
     scores: configs[3] (decode logits + softmax straight from 4-bit packed keys, 32 query heads on 8 KV heads,
             131072 keys per head, one launch set per layer instance);
     qjl:    configs[4] (V2 MSE+QJL compress, then asymmetric scores for 64 queries per head, head_dim 256);
-    decode: the incremental cache (turboquant.cache.V3Cache) in a generation loop: context 8192, one token per step;
-    llama:  configs[2] shape per layer ((8, 8, 32768, 128) bf16, K6/V4, window 128, protected layers at 8 bits),
-            `--layers` layers of it (two protected, the rest not).
+    decode: the incremental cache (turboquant.cache.V3Cache) in a generation loop: context 8192, one token per step.
     """
     import turboquant as tq
-    from turboquant import batched
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except Exception:
-        pass
+    peaks = load_peaks()
     peak = float(peaks.get("hbm_gbs", 6650.0))
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     steps, warmup = args.steps, max(args.warmup, 3)
     out = {"n_gpus": 1, "steps": steps, "warmup": warmup, "higher_is_better": True, "data": "synthetic"}
     if args.workload == "scores":
-        inst = args.layers if args.layers != LAYERS else 32
+        inst = args.layers or 32
         sk, hkv, hq = 131072, 8, 32
         comps, packed, qs = [], [], []
         for l in range(inst):
@@ -218,6 +409,7 @@ def run_side_workload(args, dev):
             qs.append(torch.randn(1, hq, 1, HEAD_DIM, generator=g, device=dev))
             comps.append(comp)
             del keys
+
         def step():
             for c, p, q in zip(comps, packed, qs):
                 c.attention_scores(q, p, softmax=True)
@@ -238,6 +430,7 @@ def run_side_workload(args, dev):
         t1 = _time_steps(lambda: comp.compress(x), steps, warmup, flush)
         t2 = _time_steps(lambda: comp.asymmetric_attention_scores(q, c), steps, warmup, flush)
         n = 16 * 16384
+        tpeak = float(peaks.get("bf16_tflops_sustained", 1400.0))
         out.update(metric="V2 MSE+QJL: vectors/s compress, keys/s scored (64 queries)", unit="vectors/s",
                    value=n * steps / t1, ms_per_step=1e3 * t1 / steps, dtype="f32",
                    config={"workload": "configs[4]: (1,16,16384,256) fp16, 3-bit TurboQuantCompressorV2, 64 queries/head"},
@@ -245,25 +438,24 @@ def run_side_workload(args, dev):
                    scores={"keys/s": n * steps / t2, "GB/s": n * 1026 * steps / t2 / 1e9, "ms": 1e3 * t2 / steps,
                            "frac_of_hbm_peak": n * 1026 * steps / t2 / 1e9 / peak,
                            "note": "tcgen05 kernel (k_umma_qjl_scores) plus its query projection and image kernels"},
-                   roofline={"bound": "tensor", "achieved": n * 393216 * steps / t1 / 1e12,
-                             "peak": float(peaks.get("bf16_tflops_sustained", 1400.0)), "unit": "TFLOP/s",
-                             "frac": n * 393216 * steps / t1 / 1e12 / float(peaks.get("bf16_tflops_sustained", 1400.0)),
-                             "traffic": None, "note": "compress = three tcgen05 contraction launches (k_umma_v2_stage); flops are "
-                                                       "the algorithmic 6 D^2 per vector, the hi/lo passes execute 2.7x "
-                                                       "that; the score kernel is HBM-bound, see scores.frac_of_hbm_peak"})
-    elif args.workload == "decode":
-        # generation loop on the incremental cache: prefill 8192 tokens per layer, then one token per step
+                   roofline={"bound": "tensor", "achieved": n * 393216 * steps / t1 / 1e12, "peak": tpeak,
+                             "unit": "TFLOP/s", "frac": n * 393216 * steps / t1 / 1e12 / tpeak, "traffic": None,
+                             "note": "compress = three tcgen05 contraction launches (k_umma_v2_stage); flops are "
+                                     "the algorithmic 6 D^2 per vector, the hi/lo passes execute 2.7x that; the "
+                                     "score kernel is HBM-bound, see scores.frac_of_hbm_peak"})
+    else:  # decode
         from turboquant.cache import V3Cache
-        nl = args.layers
-        ctx = SEQ
-        cache = V3Cache(key_bits=KEY_BITS, value_bits=VALUE_BITS, residual_window=128, protected_layers=0, n_layers=nl,
+        nl = args.layers or 36
+        ctx, heads = 8192, 2
+        cache = V3Cache(key_bits=4, value_bits=2, residual_window=128, protected_layers=0, n_layers=nl,
                         initial_capacity=ctx + 4096)
         g = torch.Generator(device=dev).manual_seed(70000)
         for l in range(nl):
-            k = torch.randn(1, KV_HEADS, ctx, HEAD_DIM, generator=g, device=dev).half()
+            k = torch.randn(1, heads, ctx, HEAD_DIM, generator=g, device=dev).half()
             cache.update(k, k * 0.5, l)
-        toks = [torch.randn(1, KV_HEADS, 1, HEAD_DIM, generator=g, device=dev).half() for _ in range(8)]
+        toks = [torch.randn(1, heads, 1, HEAD_DIM, generator=g, device=dev).half() for _ in range(8)]
         it = [0]
+
         def step():
             t = toks[it[0] % len(toks)]
             it[0] += 1
@@ -273,42 +465,14 @@ def run_side_workload(args, dev):
         out.update(metric="decode-step cache updates/s (one new token appended to every layer, oldest window token "
                           "quantised and reconstructed in place)", unit="layer-updates/s", value=nl * steps / t,
                    ms_per_step=1e3 * t / steps, dtype="f16xf16->f32",
-                   config={"workload": f"incremental cache, {nl} layers x {KV_HEADS} KV heads, context {ctx}, K4/V2, "
+                   config={"workload": f"incremental cache, {nl} layers x {heads} KV heads, context {ctx}, K4/V2, "
                                        "residual_window=128; host-side call overhead included"},
                    roofline={"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None,
                              "traffic": None, "note": "latency path: two small launches per layer"})
-    else:  # llama
-        nl = args.layers if args.layers != LAYERS else 4
-        idxs = ([0, 1] + list(range(10, 10 + nl)))[:nl] if nl > 2 else list(range(nl))
-        codecs = [tq.TurboQuantV3(HEAD_DIM, key_bits=6, value_bits=4, residual_window=128, layer_idx=l, n_layers=32,
-                                  protected_layers=4, device=dev) for l in idxs]
-        keys, vals = [], []
-        for l in idxs:
-            g = torch.Generator(device=dev).manual_seed(30000 + l)
-            k = torch.randn(8, 8, 32768, HEAD_DIM, generator=g, device=dev, dtype=torch.bfloat16)
-            v = torch.randn(8, 8, 32768, HEAD_DIM, generator=g, device=dev, dtype=torch.bfloat16)
-            k[:, :, :, :4] *= 10.0
-            keys.append(k)
-            vals.append(v)
-        plan = batched.CachePlan(codecs, keys, vals)
-        tq_ = _time_steps(plan.compress, steps, warmup, flush)
-        td_ = _time_steps(plan.decompress, steps, warmup, flush)
-        n = nl * 2 * 8 * 8 * (32768 - 128)
-        by = sum(8 * 8 * (32768 - 128) * (256 + (128 * b + 7) // 8 // (1 if b > 4 else 1) * 0 + (128 // (8 // b)) + 2)
-                 for c in codecs for b in (c.key_bits, c.value_bits))
-        out.update(metric=METRIC, unit="vectors/s", value=n * steps / (tq_ + td_), ms_per_step=1e3 * (tq_ + td_) / steps,
-                   dtype="bf16xbf16->f32",
-                   config={"workload": f"configs[2] shape, {nl} layers (indices {idxs}): (8,8,32768,128) bf16, K6/V4, "
-                                       "residual_window=128, protected_layers=4 at 8 bits"},
-                   roofline={"bound": "hbm", "achieved": by * steps / tq_ / 1e9, "peak": peak, "unit": "GB/s",
-                             "frac": by * steps / tq_ / 1e9 / peak, "traffic": None,
-                             "phases": {"quantize": {"ms": 1e3 * tq_ / steps, "GB/s": by * steps / tq_ / 1e9,
-                                                     "frac": by * steps / tq_ / 1e9 / peak},
-                                        "dequantize": {"ms": 1e3 * td_ / steps, "GB/s": by * steps / td_ / 1e9,
-                                                       "frac": by * steps / td_ / 1e9 / peak}}})
     print(json.dumps(out))
 
 
+# ----------------------------------------------------------------------------- main arm
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -316,11 +480,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="kv", choices=["kv", "scores", "qjl", "llama", "decode"],
-                    help="kv = the headline workload (configs[1]); the others measure further rows of the path on 1 GPU")
-    ap.add_argument("--layers", type=int, default=LAYERS, help="layers per rank (smaller values are for profiling only)")
-    ap.add_argument("--key-bits", type=int, default=KEY_BITS, help="profiling only; the headline workload is K4")
-    ap.add_argument("--value-bits", type=int, default=VALUE_BITS, help="profiling only; the headline workload is V2")
+    ap.add_argument("--no-e2e", action="store_true", help="profiling only: skip the host round trip")
+    ap.add_argument("--no-parity", action="store_true", help="profiling only: skip the oracle check of the timed buffers")
+    ap.add_argument("--workload", default="kv", choices=["kv", "qwen", "scores", "qjl", "decode"],
+                    help="kv = the headline workload (configs[2]); qwen = configs[1]; the others measure further "
+                         "rows of the path on 1 GPU")
+    ap.add_argument("--layers", type=int, default=0, help="profiling only: use the first and last layers/2 of the "
+                                                          "cache (keeps the mix of protected and ordinary layers)")
+    ap.add_argument("--seq", type=int, default=0, help="profiling only: shorter sequence")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -340,20 +507,42 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     lib = _native.lib()
-    n_layers = args.layers
-    if args.workload != "kv":
+    refuse_profiling_switches(lib)
+    if args.workload not in CACHES:
         if rank == 0:
             run_side_workload(args, dev)
         return
 
-    kb, vb = args.key_bits, args.value_bits
-    codecs = [tq.TurboQuantV3(HEAD_DIM, key_bits=kb, value_bits=vb, residual_window=0, layer_idx=l,
-                              n_layers=LAYERS, protected_layers=0, device=dev) for l in range(n_layers)]
-    keys = [synthetic_layer(dev, 20000 + 100000 * rank + l) for l in range(n_layers)]
-    vals = [synthetic_layer(dev, 25000 + 100000 * rank + l) for l in range(n_layers)]
-    vectors_per_step = 2 * n_layers * KV_HEADS * SEQ
-    bytes_q = n_layers * KV_HEADS * SEQ * (algorithmic_bytes_per_vector(kb) + algorithmic_bytes_per_vector(vb))
-    bytes_d = bytes_q
+    cfg = dict(CACHES[args.workload])
+    reduced = False
+    if args.seq:
+        cfg["seq"], reduced = args.seq, True
+    if args.layers and args.layers < cfg["layers"]:
+        reduced = True
+    layers = rank_layers(cfg, rank, world)
+    if args.layers and args.layers < cfg["layers"]:
+        half = max(args.layers // 2, 1)
+        layers = layers[:half] + layers[len(layers) - (args.layers - half):]
+    B, S, W = cfg["batch"], cfg["seq"], cfg["window"]
+    elem = 2
+    codecs = [tq.TurboQuantV3(HEAD_DIM, key_bits=cfg["key_bits"], value_bits=cfg["value_bits"],
+                              residual_window=W, layer_idx=l, n_layers=cfg["layers"],
+                              protected_layers=cfg["protected"], device=dev) for l, _ in layers]
+    keys = [synthetic_layer(cfg, l, 0, heads, dev) for l, heads in layers]
+    vals = [synthetic_layer(cfg, l, 1, heads, dev) for l, heads in layers]
+    q_tokens = S - W if S > W else 0
+    # per width class: quantised vectors and algorithmic bytes of this rank
+    classes = {}
+    for (l, heads), codec in zip(layers, codecs):
+        for bits in (codec.key_bits, codec.value_bits):
+            c = classes.setdefault(bits, {"vectors": 0, "bytes": 0})
+            n = B * len(heads) * q_tokens
+            c["vectors"] += n
+            c["bytes"] += n * algorithmic_bytes_per_vector(bits, elem)
+    vectors_rank = sum(c["vectors"] for c in classes.values())
+    bytes_q = sum(c["bytes"] for c in classes.values())
+    window_tokens = sum(2 * B * len(heads) * min(W, S) for l, heads in layers) if q_tokens else 0
+    bytes_d = bytes_q + window_tokens * 2 * HEAD_DIM * elem        # the dequantise phase also copies the window tokens
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # larger than the 126 MB L2
 
     def barrier():
@@ -374,7 +563,7 @@ def main():
         flush.zero_()
         if ev:
             ev[2].record()
-        plan.decompress()
+        plan.decompress()                               # window copy + dequantise
         if ev:
             ev[3].record()
 
@@ -383,105 +572,157 @@ def main():
     events = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     barrier()
     launches0 = lib.tq_launch_count()
-    with ClockSampler(local_rank) as clocks:
+    clocks = ClockSampler(local_rank)
+    with clocks:
         for s in range(args.steps):
             one_step(events[s])
         barrier()
     launches = lib.tq_launch_count() - launches0
     t_q = sum(e[0].elapsed_time(e[1]) for e in events) * 1e-3
     t_d = sum(e[2].elapsed_time(e[3]) for e in events) * 1e-3
-    total = torch.tensor([t_q + t_d, t_q, t_d], dtype=torch.float64, device=dev)
+    sums = torch.tensor([t_q + t_d, t_q, t_d], dtype=torch.float64, device=dev)
+    counts = torch.tensor([vectors_rank, bytes_q, bytes_d], dtype=torch.float64, device=dev)
     if world > 1:
-        dist.all_reduce(total, op=dist.ReduceOp.MAX)
-    t_all, t_q, t_d = total.tolist()
+        dist.all_reduce(sums, op=dist.ReduceOp.MAX)
+        dist.all_reduce(counts, op=dist.ReduceOp.SUM)
+    t_all, t_q, t_d = sums.tolist()
+    vectors_all, bytes_q_all, bytes_d_all = counts.tolist()
+
+    # ---- per width class, this rank, outside the headline interval: the same kernels on the layers of one class
+    class_times = {}
+    if rank == 0:
+        groups = {}
+        for i, codec in enumerate(codecs):
+            groups.setdefault((codec.key_bits, codec.value_bits), []).append(i)
+        for kv_bits, idxs in groups.items():
+            runs = []                                  # contiguous layer ranges of this class
+            for i in idxs:
+                if runs and runs[-1][1] == i:
+                    runs[-1][1] = i + 1
+                else:
+                    runs.append([i, i + 1])
+            nvec = sum(B * len(layers[i][1]) * q_tokens for i in idxs)
+            by = sum(nvec * algorithmic_bytes_per_vector(b, elem) for b in kv_bits)
+            tq_c = _time_steps(lambda: [plan.compress(a, b) for a, b in runs], 3, 1, flush)
+            td_c = _time_steps(lambda: [plan.decompress(a, b) for a, b in runs], 3, 1, flush)
+            class_times[f"K{kv_bits[0]}/V{kv_bits[1]}"] = {
+                "layers": len(idxs), "vectors": 2 * nvec, "algorithmic_bytes": by,
+                "quantize": {"ms": 1e3 * tq_c / 3, "GB/s": by * 3 / tq_c / 1e9},
+                "dequantize": {"ms": 1e3 * td_c / 3, "GB/s": by * 3 / td_c / 1e9}}
+        one_step()                                      # leave the buffers as a whole-cache step produces them
 
     # ---- end to end through the public API from pinned host memory ------------
-    h_keys = [k.cpu().pin_memory() for k in keys]
-    h_vals = [v.cpu().pin_memory() for v in vals]
-    e2e_steps = max(1, min(args.steps, 5))
-    streamed = batched.HostStreamedCache(codecs, h_keys, h_vals, dev, groups=6)
-
-    def e2e_step():
-        streamed.run()        # h2d copies, quantize, dequantize, d2h copies: pipelined over layer groups
-
-    e2e_step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks_e2e:       # the second measured region; samples are pooled below
-        e0.record()
-        for _ in range(e2e_steps):
-            e2e_step()
-        e1.record()
+    e2e = None
+    if not args.no_e2e:
+        h_keys = [torch.empty(k.shape, dtype=k.dtype, pin_memory=True) for k in keys]
+        h_vals = [torch.empty(v.shape, dtype=v.dtype, pin_memory=True) for v in vals]
+        for h, d in zip(h_keys + h_vals, keys + vals):
+            h.copy_(d)
+        groups_n = max(1, min(len(codecs), 16))
+        streamed = batched.HostStreamedCache(codecs, h_keys, h_vals, dev, groups=groups_n, plan=plan,
+                                             dev_keys=keys, dev_values=vals)
+        e2e_steps = args.steps
+        streamed.run()
         barrier()
-    clocks.samples += clocks_e2e.samples
-    clocks.reasons |= clocks_e2e.reasons
-    t_e2e = torch.tensor([e0.elapsed_time(e1) * 1e-3], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
-    t_e2e = float(t_e2e.item())
-    io_bytes = streamed.h2d_bytes
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with clocks:                                    # the second measured region; samples are pooled
+            e0.record()
+            for _ in range(e2e_steps):
+                streamed.run()
+            e1.record()
+            barrier()
+        # copy-only floor: the same pinned H2D + D2H traffic at the same N with no kernels
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        copy_steps = max(1, min(e2e_steps, 3))
+        streamed.run(kernels=False)
+        barrier()
+        c0.record()
+        for _ in range(copy_steps):
+            streamed.run(kernels=False)
+        c1.record()
+        barrier()
+        tt = torch.tensor([e0.elapsed_time(e1) * 1e-3 / e2e_steps, c0.elapsed_time(c1) * 1e-3 / copy_steps],
+                          dtype=torch.float64, device=dev)
+        io = torch.tensor([streamed.h2d_bytes], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            dist.all_reduce(io, op=dist.ReduceOp.SUM)
+        t_e2e, t_copy = tt.tolist()
+        streamed.run()                                  # real contents back in the buffers for the parity check
+        torch.cuda.synchronize()
+        e2e = {"value": vectors_all / t_e2e, "unit": "vectors/s", "h2d_bytes_per_step": int(io.item()),
+               "d2h_bytes_per_step": int(io.item()), "steps": e2e_steps, "ms_per_step": 1e3 * t_e2e,
+               "copy_only_ms_per_step": 1e3 * t_copy, "frac_of_copy_only_floor": t_copy / t_e2e,
+               "host_link_GBs_each_way": io.item() / t_copy / 1e9,
+               "what": "HostStreamedCache.run(): pinned host K,V -> device -> compress -> decompress -> pinned host "
+                       f"K,V, {groups_n} layer groups per rank pipelined over three streams (copies in, kernels, copies "
+                       "out); copy_only = the same copies with no kernels, same ranks running"}
+        del h_keys, h_vals
+
+    parity = None
+    if not args.no_parity and rank == 0:
+        parity = parity_block(cfg, layers, keys, vals, plan)
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except Exception:
-        pass
+    peaks = load_peaks()
     peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
     peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
-    ach_q = bytes_q * args.steps / t_q / 1e9
-    ach_d = bytes_d * args.steps / t_d / 1e9
-    # one-directional ceilings: quantize mostly reads (16-bit vectors in), dequantize mostly writes
+    # achieved = algorithmic bytes of all ranks / max-over-ranks time, per GPU
+    ach_q = bytes_q_all * args.steps / t_q / 1e9 / world
+    ach_d = bytes_d_all * args.steps / t_d / 1e9 / world
     ceil = directional_ceilings(flush)
-    big = n_layers * KV_HEADS * SEQ * 2 * HEAD_DIM * 2          # 16-bit vectors, K and V
-    small = bytes_q - big                                        # packed rows + norms
-    def floor_ms(rd, wr):
-        return 1e3 * max(rd / ceil["read_only"], wr / ceil["write_only"], (rd + wr) / ceil["copy"]) / 1e9
-    floor_q, floor_d = floor_ms(big, small), floor_ms(small, big)
-    dominant = ("quantize", ach_q, t_q) if t_q >= t_d else ("dequantize", ach_d, t_d)
+    dominant = ("quantize (k_umma_quantize)", ach_q, t_q) if t_q >= t_d else ("dequantize (k_umma_dequantize)", ach_d, t_d)
+    for c in class_times.values():
+        for ph in ("quantize", "dequantize"):
+            c[ph]["frac"] = c[ph]["GB/s"] / peak_gbs
+    traffic = None
+    key = "quantize" if t_q >= t_d else "dequantize"
+    if (args.workload, key) in NCU_DRAM_BYTES_PER_VECTOR and not reduced:
+        traffic = NCU_DRAM_BYTES_PER_VECTOR[(args.workload, key)] * vectors_rank
     out = {
-        "metric": METRIC, "value": world * vectors_per_step * args.steps / t_all, "unit": "vectors/s", "n_gpus": world,
+        "metric": METRIC, "value": vectors_all * args.steps / t_all, "unit": "vectors/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_all / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "layers_per_gpu": n_layers, "units_per_gpu": n_layers * KV_HEADS,
-                   "vectors_per_step_per_gpu": vectors_per_step,
+        "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16xbf16->f32" if cfg["dtype"] == torch.bfloat16 else "f16xf16->f32", "data": "synthetic",
+        "config": {"workload": cfg["name"] + (" [reduced for profiling]" if reduced else ""),
+                   "partition": f"{cfg['layers'] * cfg['kv_heads']} (layer, KV head) units in contiguous blocks over "
+                                f"{world} rank(s), no collective on the data path",
+                   "rank0_layers": len(layers), "vectors_per_step": int(vectors_all),
                    "l2": "a 256 MiB buffer is overwritten before each phase (outside the event-timed intervals); "
-                         "inputs and outputs (302 MB each) exceed the 126 MB L2",
-                   "timing": "CUDA events around the quantize phase and the dequantize phase of every step, summed; max over ranks"},
+                         "inputs and outputs exceed the 126 MB L2",
+                   "timing": "CUDA events around the quantize phase and the dequantize phase (window copy + "
+                             "dequantise) of every step, summed; max over ranks"},
         "roofline": {"bound": "hbm", "kernel": dominant[0], "achieved": dominant[1], "peak": peak_gbs, "unit": "GB/s",
-                     "frac": dominant[1] / peak_gbs, "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(dominant[0]) if
-                     (n_layers == LAYERS and kb == KEY_BITS and vb == VALUE_BITS) else None,
-                     "traffic_source": "ncu dram__bytes_read+write of an 18-layer capture x2 (profiles/)",
+                     "frac": dominant[1] / peak_gbs, "traffic": traffic,
+                     "traffic_source": "ncu dram__bytes_read+write of a shorter-sequence capture of the same launch, "
+                                       "scaled by the vectors processed",
                      "peak_source": peak_src,
                      "phases": {"quantize": {"GB/s": ach_q, "frac": ach_q / peak_gbs, "ms": 1e3 * t_q / args.steps,
-                                             "algorithmic_bytes": bytes_q, "directional_floor_ms": floor_q,
-                                             "frac_of_directional_floor": floor_q / (1e3 * t_q / args.steps)},
+                                             "algorithmic_bytes": int(bytes_q_all)},
                                 "dequantize": {"GB/s": ach_d, "frac": ach_d / peak_gbs, "ms": 1e3 * t_d / args.steps,
-                                               "algorithmic_bytes": bytes_d, "directional_floor_ms": floor_d,
-                                               "frac_of_directional_floor": floor_d / (1e3 * t_d / args.steps)}},
+                                               "algorithmic_bytes": int(bytes_d_all)}},
+                     "width_classes_rank0": class_times,
                      "directional_ceilings_GBs": ceil,
                      "directional_note": "read-only / write-only / copy bandwidth measured in this run with torch "
-                                         "kernels; floor = max(read bytes / read-only, write bytes / write-only, "
-                                         "all bytes / copy)"},
-        "e2e": {"value": world * vectors_per_step * e2e_steps / t_e2e, "unit": "vectors/s",
-                "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes, "steps": e2e_steps,
-                "ms_per_step": 1e3 * t_e2e / e2e_steps,
-                "what": "HostStreamedCache.run(): pinned host fp16 K,V -> device -> compress -> decompress -> pinned host fp16 K,V, "
-                        "6 layer groups pipelined over three streams (copies in, kernels, copies out)"},
+                                         "kernels over a 256 MiB buffer"},
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
     }
+    if e2e is not None:
+        out["e2e"] = e2e
+    if parity is not None:
+        out["parity"] = parity
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
-        v, s = cpu_reference_pass(1, threads)            # warm-up: codebooks, thread pool
-        layers = max(1, min(LAYERS, int(12.0 / max(s, 1e-3))))
-        v, s = cpu_reference_pass(layers, threads)
-        out["cpu_baseline"] = {"value": v / s, "unit": "vectors/s", "cores": threads, "kind": "port",
-                               "sample": f"{layers} of {LAYERS} layers of the same workload, one pass, {s:.1f} s"}
+        sample = CpuSample(cfg, threads, chunk_tokens=8192 if cfg["seq"] >= 8192 else cfg["seq"])
+        sample.run()                                    # warm-up: thread pool, allocator
+        s = sample.run()
+        out["cpu_baseline"] = {"value": sample.vectors_per_pass / s, "unit": "vectors/s", "cores": threads,
+                               "kind": sample.kind, "sample": sample.describe() + f"; one pass, {s:.1f} s"}
     print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

@@ -37,7 +37,7 @@ enum {
   TQ_ELAUNCH = -7,   /* the CUDA runtime refused the launch (see tq_last_cuda_error) */
   TQ_EWORKSPACE = -8,/* workspace smaller than tq_*_workspace_bytes says        */
   TQ_ETOOBIG = -9,   /* problem exceeds a fixed capacity of the entry point     */
-  TQ_EDEVICE = -10   /* device is not compute capability 10.x                   */
+  TQ_EDEVICE = -10   /* device is not compute capability 10.x, or its ordinal is not served */
 };
 
 /* element types of caller tensors */
@@ -163,6 +163,28 @@ typedef struct {
  * TurboQuantMSE.dequantize turboquant/turboquant.py:88-91 (norms NULL).        */
 int tq_dequantize(const TqDequantizeJob* jobs, int n_jobs, void* stream);
 
+/* ---- residual window: strided copy of kept 16-bit tokens ------------------ */
+typedef struct {
+  const void* src;        /* [dev] element (b,h,s,d) at src[b*sstride_b + h*sstride_h + s*sstride_s + d] */
+  void* dst;              /* [dev] same indexing with the dstride_* strides                    */
+  int32_t elem_bytes;     /* 2 or 4                                                            */
+  int32_t D;              /* contiguous last dimension; D*elem_bytes a multiple of 16          */
+  int64_t B, H, S;
+  int64_t sstride_b, sstride_h, sstride_s;   /* in elements; byte strides multiples of 16      */
+  int64_t dstride_b, dstride_h, dstride_s;
+} TqCopyJob;
+
+/* Copies n_jobs blocks of rows in one launch: the kept window tokens of every layer's K and
+ * V into the buffers tq_dequantize writes the reconstructed tokens into.  src and dst are
+ * 16-byte aligned and do not overlap.
+ * Replaces: the torch.cat with the "fp16" part in TurboQuantV3.decompress_kv
+ * turboquant/compressors_v3.py:230-232.                                        */
+int tq_copy_rows(const TqCopyJob* jobs, int n_jobs, void* stream);
+
+/* 1 when the library was built with -DTQ_ABLATION (timing-only switches that skip parts
+ * of the kernels, selected by the TQ_ABLATE environment variable), 0 for a normal build. */
+int tq_ablation_build(void);
+
 /* ---- generic projection: out = x @ m ---------------------------------- */
 /* x [dev] (n, K) contiguous of x_dtype; m [dev] (K, N) row-major fp32; out (n, N) fp32.
  * K, N in 1..256.  Replaces: TurboQuantMSE.rotate/unrotate
@@ -211,6 +233,10 @@ int tq_score_packed(const TqScoreJob* job, void* stream);
  * call's contents (nothing in it needs clearing); two calls whose kernels can
  * overlap on the GPU -- different streams without an ordering between them --
  * race on it, so keep such calls on one stream or order them with events.
+ * The looked-up address is kept until the process exits: after cudaDeviceReset,
+ * or once the device's primary context has been destroyed, it is stale and the
+ * entry point must not be used again in that process.  Device ordinals of 64
+ * and above are not served (TQ_EDEVICE).
  * This entry point has no counterpart in the reference.                       */
 #define TQ_SCORE_NOALLOC_SCRATCH_BYTES (4u << 20)
 int tq_score_packed_noalloc(const TqScoreJob* job, void* stream);

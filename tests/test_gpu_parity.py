@@ -1,11 +1,9 @@
 """GPU parity: the CUDA path (through the Python mirror, i.e. through the C ABI)
 against the CPU oracle on the same seeded inputs and against the golden fixtures.
 
-Tolerances (the ones the task states):
-  * rotated fp32 values in -> packed bytes: bit exact;
-  * end to end: index agreement >= 99.99 %, every mismatch within 1e-6 of a
-    decision boundary; fp16 norms within 1 ulp;
-  * reconstructions and scores: <= 1e-5 relative (fp32 I/O), <= 2e-3 (16-bit I/O).
+Tolerances: see tests/parity_helpers.py (bit exact from rotated values; every end-to-end
+index mismatch attributed to a decision boundary and bounded by count; fp16 norms within
+1 ulp; <= 1e-5 relative for fp32 I/O, <= 2e-3 of the vector's largest value for 16-bit I/O).
 """
 
 import numpy as np
@@ -14,6 +12,7 @@ import torch
 
 import tq_oracle as O
 from conftest import bits16, from_bits16, load_golden
+from parity_helpers import check_indices, check_norms, check_recon_16bit, check_v2_compress, rel_err
 
 import turboquant as tq
 from turboquant import _native as N
@@ -23,31 +22,20 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def rel_err(got, want):
-    got, want = got.detach().float().cpu(), want.detach().float().cpu()
-    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+def few_neighbour_mismatches(mine, gold, k=2):
+    """Indices against bytes the reference stored (its rotation matrix comes out of LAPACK QR and may differ in
+    the last bits from the one rebuilt here): neighbouring indices only, at most k of them."""
+    d = np.abs(np.asarray(mine).astype(np.int64) - np.asarray(gold).astype(np.int64))
+    assert d.max() <= 1 and int((d != 0).sum()) <= k, (int(d.max()), int((d != 0).sum()))
+    return (d != 0).reshape(d.shape[0], -1).any(-1)          # rows that hold a mismatch
 
 
-def check_indices(got_packed, x_cpu, pi, cent, bnd, bits, d, min_agree=0.9999):
-    """Compare packed indices with the oracle; mismatches must sit on a decision boundary."""
-    _flat, norms, rot = O.rotate_unit(x_cpu, pi)
-    want = O.nearest_centroid(rot, cent).numpy()
-    n = want.shape[0]
-    got = O.unpack_indices(got_packed.cpu().numpy().reshape(n, -1), bits, d)
-    bad = np.argwhere(got != want)
-    for r, c in bad[:2000]:
-        y = rot[r, c].item()
-        assert abs(int(got[r, c]) - int(want[r, c])) == 1, (r, c, got[r, c], want[r, c])
-        assert np.min(np.abs(bnd.numpy() - y)) < 1e-6, (r, c, y)
-    agree = 1.0 - len(bad) / want.size
-    assert agree >= min_agree, agree
-    return norms, agree
-
-
-def check_norms(got_fp16, want_fp32):
-    g = bits16(got_fp16).astype(np.int32).reshape(-1)
-    w = bits16(want_fp32.to(torch.float16)).astype(np.int32).reshape(-1)
-    assert np.all(np.abs(g - w) <= 1)
+def signs_equal_outside(mine, gold, rows_excluded, k=2):
+    """QJL signs equal the stored ones on every row without an index mismatch, except for at most k coordinates
+    (projections that are numerically zero)."""
+    diff = (np.asarray(mine) != np.asarray(gold)).reshape(len(rows_excluded), -1)
+    assert int(diff[~rows_excluded].sum()) <= k, int(diff[~rows_excluded].sum())
 
 
 # --------------------------------------------------------------------------- K0
@@ -107,9 +95,11 @@ def test_cfg1_roundtrip_against_oracle_and_golden():
         assert c["shape"] == (1, 1, 4096, 128) and c["idx_pad"] == 0
         norms, agree = check_indices(c["idx_bytes"], x, comp.Pi.cpu(), cent, bnd, bits, 128)
         check_norms(c["vec_norms"], norms)
-        gold_agree = (O.unpack_indices(c["idx_bytes"].cpu().numpy().reshape(4096, -1), bits, 128)
-                      == O.unpack_indices(z[f"{tag}_idx"].reshape(4096, -1), bits, 128)).mean()
-        assert gold_agree >= 0.9999
+        # against the bytes the reference itself stored (its rotation matrix comes out of LAPACK QR and may
+        # differ in the last bits from the one rebuilt here): at most 1e-4 of the coordinates, neighbours only
+        mine = O.unpack_indices(c["idx_bytes"].cpu().numpy().reshape(4096, -1), bits, 128).astype(np.int32)
+        gold = O.unpack_indices(z[f"{tag}_idx"].reshape(4096, -1), bits, 128).astype(np.int32)
+        assert np.abs(mine - gold).max() <= 1 and (mine != gold).sum() <= int(np.ceil(1e-4 * gold.size))
         rec = comp.decompress(c)
         assert rec.dtype == torch.float32 and rec.shape == (1, 1, 4096, 128)
         want = O.mse_decompress({k: (v.cpu() if torch.is_tensor(v) else v) for k, v in c.items()}, comp.Pi.cpu(), cent, bits)
@@ -129,7 +119,7 @@ def test_small_cases_every_bits_and_head_dim_including_padding():
         cent, bnd = O.lloyd_max(d, bits)
         c = comp.compress(x.to(DEV))
         assert c["idx_pad"] == int(z[f"pad_{k}"]) and tuple(c["idx_bytes"].shape) == z[f"idx_{k}"].shape
-        norms, _ = check_indices(c["idx_bytes"], x, comp.Pi.cpu(), cent, bnd, bits, d, min_agree=0.999)
+        norms, _ = check_indices(c["idx_bytes"], x, comp.Pi.cpu(), cent, bnd, bits, d)
         check_norms(c["vec_norms"], norms)
         gold = {"idx_bytes": torch.from_numpy(z[f"idx_{k}"]).to(DEV), "vec_norms": from_bits16(z[f"norms_{k}"], torch.float16).to(DEV),
                 "shape": tuple(x.shape), "idx_pad": int(z[f"pad_{k}"])}
@@ -195,7 +185,7 @@ def test_empty_and_tiny_inputs():
         x = torch.randn(1, 1, n, 128, generator=torch.Generator().manual_seed(n))
         c = comp.compress(x.to(DEV))
         cent, bnd = O.lloyd_max(128, 4)
-        check_indices(c["idx_bytes"], x, comp.Pi.cpu(), cent, bnd, 4, 128, min_agree=0.999)
+        check_indices(c["idx_bytes"], x, comp.Pi.cpu(), cent, bnd, 4, 128)
 
 
 def test_scale_invariance_and_idempotence_at_full_layer_size():
@@ -243,20 +233,21 @@ def test_v3_compress_decompress_kv_against_golden(tag):
         for c, nm, bits, comp in ((ck, "k", codec.key_bits, codec.key_compressor), (cv, "v", codec.value_bits, codec.val_compressor)):
             src = (keys if nm == "k" else vals)[:, :, :cut, :].cpu().contiguous()
             cent, bnd = O.lloyd_max(128, bits)
-            norms, _ = check_indices(c["compressed"]["idx_bytes"], src, comp.Pi.cpu(), cent, bnd, bits, 128, min_agree=0.9995)
+            norms, _ = check_indices(c["compressed"]["idx_bytes"], src, comp.Pi.cpu(), cent, bnd, bits, 128)
             check_norms(c["compressed"]["vec_norms"], norms)
             gold = O.unpack_indices(z[f"{tag}_{nm}_idx"].reshape(-1, z[f"{tag}_{nm}_idx"].shape[-1]), bits, 128)
             mine = O.unpack_indices(c["compressed"]["idx_bytes"].cpu().numpy().reshape(gold.shape[0], -1), bits, 128)
-            assert (gold == mine).mean() >= 0.999
+            diff = np.abs(gold.astype(np.int32) - mine.astype(np.int32))
+            assert diff.max() <= 1 and (diff != 0).sum() <= max(2, int(np.ceil(1e-4 * gold.size)))
     rk, rv = codec.decompress_kv(ck, cv)
     assert rk.dtype == dt and rk.shape == keys.shape and rv.shape == vals.shape
     for got, want in ((rk, from_bits16(z[f"{tag}_rk"], dt)), (rv, from_bits16(z[f"{tag}_rv"], dt))):
-        if dt == torch.float16:
-            assert rel_err(got, want) <= 2e-3
-        else:   # bf16 cannot express 2e-3: one bf16 ulp of the largest value, and a small mean error
-            w, g = want.float(), got.float().cpu()
-            assert float((g - w).abs().max()) <= 2.0 ** -7 * float(w.abs().max())
-            assert float((g - w).abs().mean()) <= 2e-3 * float(w.abs().mean())
+        # the fixture holds the reference's own 16-bit output: per vector within 2e-3 of the largest value
+        # plus the final rounding of the format (one unit in the last place between two roundings)
+        g, w = got.float().cpu(), want.float()
+        eps = 2.0 ** -7 if dt == torch.bfloat16 else 2.0 ** -10
+        bound = 2e-3 * w.abs().amax(-1, keepdim=True) + eps * w.abs() + 1e-30
+        assert bool(((g - w).abs() <= bound).all()), float(((g - w).abs() / bound).max())
     if tag != "d":
         cut = ck["split_at"]
         assert torch.equal(rk[:, :, cut:], keys[:, :, cut:]) and torch.equal(rv[:, :, cut:], vals[:, :, cut:])
@@ -321,11 +312,7 @@ def test_v2_compress_and_scores_against_golden():
         c = comp.compress(x.to(DEV))
         assert c["k_mse"].dtype == torch.float16 and c["qjl_signs"].dtype == torch.int8
         assert c["residual_norm"].dtype == torch.float16 and c["shape"] == tuple(x.shape)
-        want = O.v2_compress(x, comp.Pi.cpu(), comp.centroids.cpu(), comp.S.cpu())
-        assert rel_err(c["k_mse"], want["k_mse"]) <= 2e-3
-        assert (c["qjl_signs"].cpu() == want["qjl_signs"]).float().mean() >= 0.999
-        assert set(c["qjl_signs"].unique().tolist()) <= {-1, 1}
-        check_norms(c["residual_norm"], want["residual_norm"].float())
+        check_v2_compress(c, x, comp.Pi.cpu(), comp.centroids.cpu(), comp.S.cpu())
         gold = {"k_mse": from_bits16(z[f"{tag}_kmse"], torch.float16).to(DEV), "qjl_signs": torch.from_numpy(z[f"{tag}_signs"]).to(DEV),
                 "residual_norm": from_bits16(z[f"{tag}_rnorm"], torch.float16).to(DEV), "shape": tuple(x.shape)}
         sc = comp.asymmetric_attention_scores(q.to(DEV), gold)
@@ -334,7 +321,7 @@ def test_v2_compress_and_scores_against_golden():
     comp = tq.TurboQuantCompressorMSE(128, 2, seed=9, device=DEV)
     c = comp.compress(x.to(DEV))
     assert c["indices"].dtype == torch.uint8 and tuple(c["indices"].shape) == (64, 128) and c["vec_norms"].shape == (64,)
-    assert (c["indices"].cpu().numpy() == z["m_idx"]).mean() >= 0.9995
+    few_neighbour_mismatches(c["indices"].cpu().numpy(), z["m_idx"])
     gold = {"indices": torch.from_numpy(z["m_idx"]).to(DEV), "vec_norms": from_bits16(z["m_norms"], torch.float16).to(DEV),
             "shape": (1, 2, 32, 128)}
     assert rel_err(comp.decompress(gold), torch.from_numpy(z["m_rec"])) <= 1e-5
@@ -364,7 +351,7 @@ def test_v1_classes_against_golden():
     assert rel_err(mse.rotate(x.to(DEV)), torch.from_numpy(z["mse_rot"])) <= 1e-5
     xh, idx = mse(x.to(DEV))
     assert idx.dtype == torch.int64 and idx.shape == (32, 128)
-    assert (idx.cpu().numpy() == z["mse_idx"]).mean() >= 0.9995
+    few_neighbour_mismatches(idx.cpu().numpy(), z["mse_idx"])
     assert rel_err(mse.dequantize(torch.from_numpy(z["mse_idx"]).to(DEV)), torch.from_numpy(z["mse_xhat"])) <= 1e-5
     assert rel_err(mse.unrotate(mse.rotate(x.to(DEV))), x) <= 1e-5
     one = mse.quantize(x[0].to(DEV))
@@ -374,9 +361,9 @@ def test_v1_classes_against_golden():
     c = prod.quantize(x.to(DEV))
     assert c["mse_indices"].dtype == torch.int64 and c["qjl_signs"].dtype == torch.float32
     assert c["qjl_signs"].shape == (32, 128) and c["residual_norm"].shape == (32,)
-    assert (c["mse_indices"].cpu().numpy() == z["prod_idx"]).mean() >= 0.9995
-    assert (c["qjl_signs"].cpu().numpy() == z["prod_signs"]).mean() >= 0.999
-    assert np.allclose(c["residual_norm"].cpu().numpy(), z["prod_rnorm"], rtol=1e-4)
+    rows = few_neighbour_mismatches(c["mse_indices"].cpu().numpy(), z["prod_idx"])
+    signs_equal_outside(c["qjl_signs"].cpu().numpy(), z["prod_signs"], rows)
+    assert np.allclose(c["residual_norm"].cpu().numpy()[~rows], z["prod_rnorm"][~rows], rtol=1e-4)
     gold = {"mse_indices": torch.from_numpy(z["prod_idx"]).to(DEV), "qjl_signs": torch.from_numpy(z["prod_signs"]).to(DEV),
             "residual_norm": torch.from_numpy(z["prod_rnorm"]).to(DEV)}
     ip = prod.inner_product(y.to(DEV), gold)
@@ -389,7 +376,7 @@ def test_v1_classes_against_golden():
     prod64 = tq.TurboQuantProd(128, 4, qjl_dim=64, seed=3, device=DEV)
     c64 = prod64.quantize(x.to(DEV))
     assert c64["qjl_signs"].shape == (32, 64)
-    assert (c64["qjl_signs"].cpu().numpy() == z["prod64_signs"]).mean() >= 0.999
+    signs_equal_outside(c64["qjl_signs"].cpu().numpy(), z["prod64_signs"], np.zeros(32, dtype=bool))
     gold64 = {"mse_indices": c64["mse_indices"], "qjl_signs": torch.from_numpy(z["prod64_signs"]).to(DEV),
               "residual_norm": c64["residual_norm"]}
     assert rel_err(prod64.inner_product(y.to(DEV), gold64), torch.from_numpy(z["prod64_ip"])) <= 1e-3
@@ -541,26 +528,21 @@ def test_v2_compress_tensor_core_against_fp32_kernels(d, bits, shape):
     c = comp.compress(x.to(DEV))
     want = O.v2_compress(x, comp.Pi.cpu(), comp.centroids.cpu(), comp.S.cpu())
     assert c["k_mse"].shape == x.shape and c["qjl_signs"].shape == x.shape and c["residual_norm"].shape == x.shape[:3]
-    def vectors_close(a, b):
-        """Per vector: within 2e-3 of the tensor's scale.  A rotated value that sits on a threshold may take the
-        neighbouring index on one path (about one coordinate in 1e5), which moves that vector's k_mse, its
-        residual norm and some of its signs; all other vectors agree."""
-        a, b = a.float().cpu(), b.float().cpu()
-        return (a - b).abs().amax(-1) <= 2e-3 * float(b.abs().max())
+    marked = check_v2_compress(c, x, comp.Pi.cpu(), comp.centroids.cpu(), comp.S.cpu())
 
-    ok_vec = vectors_close(c["k_mse"], want["k_mse"])
-    assert ok_vec.float().mean() >= 0.99
-    assert rel_err(c["k_mse"], want["k_mse"]) <= 5e-2                 # a neighbouring index is a bounded error
-    assert (c["qjl_signs"].cpu() == want["qjl_signs"]).float().mean() >= 0.999
-    assert set(c["qjl_signs"].unique().tolist()) <= {-1, 1}
-    check_norms(c["residual_norm"][ok_vec.to(DEV)], want["residual_norm"].float()[ok_vec])
+    def vectors_close(a, b):
+        a, b = a.float().cpu(), b.float().cpu()
+        return (a - b).abs().amax(-1) <= 2e-3 * b.abs().amax(-1) + 1e-30
+
     os.environ["TQ_FORCE_SIMT"] = "1"
     try:
         c2 = comp.compress(x.to(DEV))
     finally:
         del os.environ["TQ_FORCE_SIMT"]
-    assert vectors_close(c["k_mse"], c2["k_mse"]).float().mean() >= 0.99
-    assert (c["qjl_signs"] == c2["qjl_signs"]).float().mean() >= 0.999
+    # the FP32 kernels as a second opinion: they may differ only on vectors with a coordinate on a boundary
+    marked2 = check_v2_compress(c2, x, comp.Pi.cpu(), comp.centroids.cpu(), comp.S.cpu())
+    differ = ~vectors_close(c["k_mse"], c2["k_mse"])
+    assert int(differ.sum()) <= marked + marked2
     from turboquant import _native
     assert _native.lib().tq_last_device_status() == 0
 
@@ -604,9 +586,7 @@ def test_v2_tensor_core_edge_shapes():
             xs = x[:, :, :s].contiguous()
             c = comp.compress(xs.to(DEV))
             want = O.v2_compress(xs, comp.Pi.cpu(), comp.centroids.cpu(), comp.S.cpu())
-            assert rel_err(c["k_mse"], want["k_mse"]) <= 2e-3
-            assert (c["qjl_signs"].cpu() == want["qjl_signs"]).float().mean() >= 0.99
-            check_norms(c["residual_norm"], want["residual_norm"].float())
+            check_v2_compress(c, xs, comp.Pi.cpu(), comp.centroids.cpu(), comp.S.cpu(), max_differing=0)
             if s == 3:
                 assert bool((c["qjl_signs"][0, 0, 1] == 1).all()) and float(c["k_mse"][0, 0, 1].abs().max()) == 0.0
             q = torch.randn(1, 1, 2, d, generator=torch.Generator().manual_seed(s))
@@ -626,6 +606,5 @@ def test_v2_compress_other_layouts_use_the_fp32_kernels():
     for x in (base[:, :, ::2], base.to(torch.bfloat16), base.float()):
         c = comp.compress(x.to(DEV) if x.is_contiguous() else base.to(DEV)[:, :, ::2])
         want = O.v2_compress(x, comp.Pi.cpu(), comp.centroids.cpu(), comp.S.cpu())
-        assert c["k_mse"].shape == x.shape and rel_err(c["k_mse"], want["k_mse"]) <= 2e-3
-        assert (c["qjl_signs"].cpu() == want["qjl_signs"]).float().mean() >= 0.999
-        check_norms(c["residual_norm"], want["residual_norm"].float())
+        assert c["k_mse"].shape == x.shape
+        check_v2_compress(c, x.contiguous(), comp.Pi.cpu(), comp.centroids.cpu(), comp.S.cpu())

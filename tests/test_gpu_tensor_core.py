@@ -13,6 +13,7 @@ import torch
 
 import tq_oracle as O
 from conftest import bits16
+from parity_helpers import check_indices, check_norms, check_recon_16bit, mismatch_budget
 
 import turboquant as tq
 from turboquant import _native as N
@@ -30,30 +31,23 @@ def _simt(fn):
         os.environ.pop("TQ_FORCE_SIMT", None)
 
 
-def _compare(c_tc, c_ref, bits, d=128, min_agree=0.9999):
+def _compare(c_tc, c_ref, bits, d=128):
+    """Tensor-core result against the FP32 kernels: neighbouring indices only, bounded by count."""
     a = O.unpack_indices(c_tc["idx_bytes"].cpu().numpy().reshape(-1, c_tc["idx_bytes"].shape[-1]), bits, d)
     b = O.unpack_indices(c_ref["idx_bytes"].cpu().numpy().reshape(-1, c_ref["idx_bytes"].shape[-1]), bits, d)
-    agree = float((a == b).mean())
-    assert agree >= min_agree, agree
-    assert np.abs(a.astype(np.int64) - b).max() <= 1
+    diff = np.abs(a.astype(np.int64) - b)
+    assert diff.max() <= 1
+    assert int((diff != 0).sum()) <= mismatch_budget(a.size), (int((diff != 0).sum()), a.size)
     g = bits16(c_tc["vec_norms"]).astype(np.int32)
     w = bits16(c_ref["vec_norms"]).astype(np.int32)
     assert np.abs(g - w).max() <= 1
 
 
-def _oracle_check(c, x_cpu, comp, bits, min_agree=0.9999):
+def _oracle_check(c, x_cpu, comp, bits):
+    """Against the oracle: every mismatch attributed to a decision boundary, bounded by count; norms 1 ulp."""
     cent, bnd = O.lloyd_max(128, bits)
-    _flat, norms, rot = O.rotate_unit(x_cpu, comp.Pi.cpu())
-    want = O.nearest_centroid(rot, cent).numpy()
-    got = O.unpack_indices(c["idx_bytes"].cpu().numpy().reshape(want.shape[0], -1), bits, 128)
-    bad = np.argwhere(got != want)
-    for r, col in bad[:2000]:
-        assert abs(int(got[r, col]) - int(want[r, col])) == 1
-        assert np.min(np.abs(bnd.numpy() - rot[r, col].item())) < 1e-6
-    assert 1.0 - len(bad) / want.size >= min_agree
-    g = bits16(c["vec_norms"]).astype(np.int32).reshape(-1)
-    w = bits16(norms.to(torch.float16)).astype(np.int32).reshape(-1)
-    assert np.abs(g - w).max() <= 1
+    norms, _ = check_indices(c["idx_bytes"], x_cpu, comp.Pi.cpu(), cent, bnd, bits, 128)
+    check_norms(c["vec_norms"], norms)
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
@@ -90,7 +84,7 @@ def test_tensor_core_tiny_and_single_row_inputs():
     for shape in ((1, 1, 1, 128), (1, 1, 127, 128), (1, 1, 128, 128), (1, 1, 129, 128), (3, 1, 5, 128), (1, 5, 2, 128)):
         x = O.synthetic_kv(shape, torch.float16, seed=sum(shape))
         c = comp.compress(x.to(DEV))
-        _oracle_check(c, x, comp, 4, min_agree=0.999)
+        _oracle_check(c, x, comp, 4)
 
 
 def test_many_layers_in_one_launch_match_per_layer_fp32_results():
@@ -125,15 +119,12 @@ def test_nan_and_zero_rows_on_the_tensor_core_path():
 
 
 # ------------------------------------------------------------------ dequantize
-def _close_16bit(got, ref, dtype):
-    """fp16: within 2e-3 of the largest value.  bf16 cannot express 2e-3 (one ulp is 2^-8..2^-7
-    of a value), so there the bar is one bf16 ulp of the largest value, plus a mean error
-    below 2e-3 so that a systematic offset cannot hide in it."""
-    g, r = got.float().cpu(), ref.float().cpu()
-    worst = float((g - r).abs().max()) / float(r.abs().max())
-    if dtype == torch.float16:
-        return worst <= 2e-3
-    return worst <= 2.0 ** -7 and float((g - r).abs().mean()) <= 2e-3 * float(r.abs().mean())
+def _close_16bit(got, ref_fp32, dtype):
+    """A 16-bit reconstruction against an fp32 one: per vector, every element within 2e-3 of the vector's
+    largest value plus the final rounding of the format (half a unit in the last place of the element)."""
+    assert got.dtype == dtype
+    check_recon_16bit(got, ref_fp32)
+    return True
 
 
 @pytest.mark.parametrize("bits", [1, 2, 3, 4, 5, 6, 7, 8])

@@ -45,6 +45,12 @@ def test_noalloc_scores_equal_the_workspace_entry_point_on_consecutive_calls():
         scale = float(want_logits.abs().max())
         assert float((logits - want_logits).abs().max()) <= 1e-5 * scale
         assert torch.allclose(probs, want_probs, rtol=2e-4, atol=1e-7)
+        # and against the CPU oracle: decompress the same packed keys, then matmul and softmax
+        cpu = {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in c.items()}
+        rec = O.mse_decompress(cpu, comp.Pi.cpu(), O.lloyd_max(128, bits)[0], bits)
+        oracle_logits = O.v3_scores(q.cpu(), rec) * 0.25
+        assert float((logits.cpu() - oracle_logits).abs().max()) <= 1e-5 * float(oracle_logits.abs().max())
+        assert torch.allclose(probs.cpu(), torch.softmax(oracle_logits, -1), rtol=2e-4, atol=1e-7)
         # logits only (probs NULL)
         only = torch.empty_like(want_logits)
         _ops.score_packed_noalloc(q, c["idx_bytes"], c["vec_norms"], comp._pi_t, comp._cb, bits, only, None, scale=0.25)

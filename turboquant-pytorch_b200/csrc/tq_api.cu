@@ -125,8 +125,8 @@ void fit_cell_table(float* block, int n) {
 
 void fit_shortcut(float* block, int n) {
   for (int i = 512; i < TQ_CODEBOOK_FLOATS; ++i) block[i] = 0.f;
-  if (n > 31 && n <= 255) { fit_cell_table(block, n); return; }
-  if (n < 1 || n > 31) return;
+  if (n > 63 && n <= 255) { fit_cell_table(block, n); return; }
+  if (n < 1 || n > 255) return;
   const float* thr = block + 256;
   const double lim = fmax(fabs((double)thr[0]), fabs((double)thr[n - 1])) * 1.001 + 1e-12;
   const float s = (float)(0.5 / lim);
@@ -171,7 +171,7 @@ void fit_shortcut(float* block, int n) {
     const int i = exact_index(y, thr, n);
     for (float sv : {s_lo, s, s_hi}) {
       const int e = shortcut_e(y, sv, c1, c2, c3);
-      if (!(e >= 0 && e <= 31 && (e == i || e + 1 == i) && (e < n || i == e))) return false;
+      if (!(e >= 0 && e <= 63 && (e == i || e + 1 == i) && (e < n || i == e))) return false;
     }
     return true;
   };
@@ -198,7 +198,10 @@ void fit_shortcut(float* block, int n) {
   int degree = 0;
   if (try_degree(1, c1, c2, c3)) degree = 1;
   else if (try_degree(n >= 3 ? 3 : n, c1, c2, c3)) degree = 3;
-  if (degree == 0) return;
+  if (degree == 0) {
+    if (n > 31) fit_cell_table(block, n);    // 6-bit codes whose cubic does not bracket: cell table
+    return;
+  }
   block[512] = 1.f;
   block[513] = s;
   block[514] = c1;
@@ -231,7 +234,7 @@ const char* tq_strerror(int code) {
     case TQ_ELAUNCH: return "CUDA launch failed";
     case TQ_EWORKSPACE: return "workspace too small";
     case TQ_ETOOBIG: return "problem exceeds the capacity of this entry point";
-    case TQ_EDEVICE: return "device is not compute capability 10.x";
+    case TQ_EDEVICE: return "device is not compute capability 10.x, or its ordinal is not served";
     default: return "unknown error code";
   }
 }
@@ -359,6 +362,34 @@ int tq_dequantize(const TqDequantizeJob* jobs, int n_jobs, void* stream) {
     if (rc != TQ_OK) return rc;
   }
   return TQ_OK;
+}
+
+int tq_ablation_build(void) {
+#ifdef TQ_ABLATION
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+int tq_copy_rows(const TqCopyJob* jobs, int n_jobs, void* stream) {
+  if (n_jobs < 0) return TQ_EINVAL;
+  if (n_jobs == 0) return TQ_OK;
+  if (jobs == nullptr) return TQ_ENULL;
+  for (int i = 0; i < n_jobs; ++i) {
+    const TqCopyJob& j = jobs[i];
+    if (j.elem_bytes != 2 && j.elem_bytes != 4) return TQ_EDTYPE;
+    if (j.D < 1 || j.B < 0 || j.H < 0 || j.S < 0) return TQ_EINVAL;
+    if (j.B * j.H * j.S == 0) continue;
+    if (j.src == nullptr || j.dst == nullptr) return TQ_ENULL;
+    const int64_t eb = j.elem_bytes;
+    if ((j.D * eb) % 16 != 0 || ((uintptr_t)j.src & 15u) || ((uintptr_t)j.dst & 15u)) return TQ_EALIGN;
+    const int64_t strides[6] = {j.sstride_b, j.sstride_h, j.sstride_s, j.dstride_b, j.dstride_h, j.dstride_s};
+    const int64_t extent[6] = {j.B, j.H, j.S, j.B, j.H, j.S};
+    for (int k = 0; k < 6; ++k)
+      if (extent[k] > 1 && (strides[k] < 0 || (strides[k] * eb) % 16 != 0)) return TQ_EALIGN;
+  }
+  return tq::copy_rows(jobs, n_jobs, (cudaStream_t)stream);
 }
 
 int tq_project(const void* x, int x_dtype, int64_t n, int K, const float* m, int N, float* out, void* stream) {

@@ -32,6 +32,9 @@ int simt_prod_inner_product(const float* y, int64_t ny, const int64_t* idx, cons
                             float* out, void* workspace, cudaStream_t st);
 
 
+// strided row copy (tq_copy.cu)
+int copy_rows(const TqCopyJob* jobs, int n_jobs, cudaStream_t st);
+
 // tensor-core path (tq_umma.cu)
 size_t umma_rotation_image_bytes(int D);
 int umma_prepare_rotation_image(const float* m, int D, void* image, cudaStream_t st);

@@ -25,12 +25,14 @@ static __device__ __align__(256) unsigned char g_score_scratch[kScratchBytes];
 std::mutex g_mu;
 void* g_scratch_ptr[kMaxDevices] = {};   // device address of g_score_scratch, per device ordinal
 
-// Resolve the array's device address once per device, with that device current.
+// Resolve the array's device address once per device, with that device current.  The address is
+// kept until the process exits: after cudaDeviceReset (or any other destruction of the device's
+// primary context) it is stale and this entry point must not be called again in the process.
 int scratch_for_current_device(void** out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) { tq::note_cuda_error((int)e); return TQ_ELAUNCH; }
-  if (dev < 0 || dev >= kMaxDevices) return TQ_ETOOBIG;
+  if (dev < 0 || dev >= kMaxDevices) return TQ_EDEVICE;    // device ordinals beyond the table below
   std::lock_guard<std::mutex> lock(g_mu);
   if (g_scratch_ptr[dev] == nullptr) {
     void* p = nullptr;

@@ -76,3 +76,36 @@ __device__ __forceinline__ void expand_half(uint32_t src, const uint32_t* lut, u
     if constexpr (PIECES == 2) st_shared_v4(dst + kTileBytes, lo[0], lo[1], lo[2], lo[3]);
   }
 }
+
+// Wide codes (one index per byte, 5..8 bits) for 16-bit outputs, which need the high fp16 piece only:
+// the table is replicated so that look-ups hardly ever collide.  Entry i (fp16 bits of the centroid)
+// is stored 32 times, copy l at byte  i * 64 + 2 * l;  lane l reads its own copy, so two lanes can
+// only meet in a bank when they form a pair (l, l ^ 1) and look up different entries of equal parity.
+// `lut_lane` is the table's shared address plus 2 * lane.
+template <int BITS>
+__device__ __forceinline__ void expand_half_wide16(uint32_t src, uint32_t lut_lane, uint32_t a_stage, int row, int half) {
+  static_assert(BITS >= 5 && BITS <= 8, "one index per byte");
+  constexpr uint32_t MASK = ((1u << BITS) - 1u) << 6;
+  uint32_t w[16];                               // 64 packed bytes: this half row
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const uint4 t = ld_shared_v4(src + 16 * v);
+    w[4 * v] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
+  }
+  const uint32_t dst_row = a_stage + half * kHalfBytes + row * 128;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    uint32_t h[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const uint32_t xw = w[2 * q + (u >> 2)];
+      const int sh = 8 * (u & 3);
+      const uint32_t off = sh >= 6 ? ((xw >> (sh - 6)) & MASK) : ((xw << (6 - sh)) & MASK);
+      uint16_t v16;
+      asm("ld.shared.u16 %0, [%1];" : "=h"(v16) : "r"(lut_lane + off));
+      h[u] = v16;
+    }
+    const uint32_t dst = dst_row + ((q ^ (row & 7)) << 4);
+    st_shared_v4(dst, h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+  }
+}

@@ -121,6 +121,20 @@ __device__ __forceinline__ void tmem_wait16(uint32_t (&r)[16]) {
                : "memory");
 }
 
+// Named barrier `id` over `count` threads that also returns the AND of `pred` over those threads.
+__device__ __forceinline__ bool bar_red_and(int id, int count, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %3, 0;\n\t"
+      "bar.red.and.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(id), "r"(count), "r"((uint32_t)pred)
+      : "memory");
+  return out != 0u;
+}
+
 // K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
   uint64_t lo = (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16);

@@ -42,21 +42,37 @@ constexpr uint32_t kTileBytes = kTileRows * kDim * 2;  // 32768
 constexpr uint32_t kHalfBytes = kTileBytes / 2;        // one 64-column box
 constexpr uint32_t kImageBytes = 5 * kTileBytes;       // fp16 hi, lo; then bf16 p0, p1, p2
 constexpr int kMaxJobs = 96;
+constexpr int kMaxCtas = 192;                          // upper bound of the grid (one CTA per SM)
+
+// Timing-only switches that skip parts of the kernels exist only in builds made with
+// -DTQ_ABLATION (build.py --ablate); the shipped library has none of these branches.
+#ifdef TQ_ABLATION
+#define TQ_ABL(batch, bits) (((batch).ablate & (bits)) != 0)
+#else
+#define TQ_ABL(batch, bits) false
+#endif
 
 // shared memory map (offsets from a 1024-byte aligned base)
-template <bool BF16>
+template <bool BF16, bool WIDE = false>
 struct Cfg {
   static constexpr int kStages = BF16 ? 3 : 4;
   static constexpr int kPieces = BF16 ? 3 : 2;
   static constexpr uint32_t kPieceOff = BF16 ? 2 * kTileBytes : 0;            // offset of the pieces in the image
   static constexpr uint32_t kOffA = 0;
   static constexpr uint32_t kOffPi = kOffA + kStages * kTileBytes;
-  static constexpr uint32_t kThrRegion = 2560;   // per epilogue warpgroup: 256 thresholds + a 1028-byte cell table
+  // Narrow launches: 256 thresholds (fp32) per epilogue warpgroup.  Launches with wide codes: ONE set of
+  // tables per CTA, shared by the four warpgroups and rebuilt at every job change (see the epilogue):
+  //   thresholds * 2^40 of 7/8-bit codes, 16 copies each (copy = lane / 2): 256 x 64 bytes,
+  //   candidate index per cell of t, 16 byte copies each:                    1025 x 16 bytes,
+  //   thresholds * 2^40 of 6-bit codes (one copy):                            64 x 4 bytes
   static constexpr uint32_t kOffThr = kOffPi + kPieces * kTileBytes;
-  static constexpr uint32_t kOffBar = kOffThr + 4 * kThrRegion;
+  static constexpr uint32_t kThrRegion = 1024;
+  static constexpr uint32_t kOffCells = kOffThr + 16384;
+  static constexpr uint32_t kOffThr6 = kOffCells + 16512;
+  static constexpr uint32_t kOffBar = WIDE ? kOffThr6 + 256 : kOffThr + 4 * kThrRegion;
   static constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;                // + alignment slack
 };
-static_assert(Cfg<false>::kSmemBytes <= 232448 && Cfg<true>::kSmemBytes <= 232448, "shared memory budget");
+static_assert(Cfg<false, true>::kSmemBytes <= 232448 && Cfg<true, true>::kSmemBytes <= 232448, "shared memory budget");
 
 struct alignas(64) UmmaQuantJob {
   CUtensorMap tmap;          // (D, S, H, B) view of x, box 64 x 128 x 1 x 1, 128-byte swizzle
@@ -77,10 +93,10 @@ struct UmmaQuantBatch {
   int32_t n_jobs;
   int32_t total_tiles;
   int32_t* status;           // device status word (may be null)
-  int32_t ablate;            // timing experiments only (TQ_ABLATE): 1 skip stores, 2 skip the epilogue, 4 skip MMA,
-                             // 16 no lane look-up, 32 half loads, 64 no loads, 128 arrive instead of commit,
-                             // 256 / 512 skip the quantise / norm sweep, 8192 MMAs as two N = 64 halves
+  int32_t ablate;            // -DTQ_ABLATION builds only (TQ_ABLATE): 1 skip stores, 2 skip the epilogue, 4 skip MMA,
+                             // 32 half loads, 64 no loads, 256 / 512 skip the quantise / norm sweep
   int32_t pad_[3];
+  int32_t cta_begin[kMaxCtas + 1];   // CTA c owns tiles [cta_begin[c], cta_begin[c + 1]): equal estimated cost, not equal count
   UmmaQuantJob jobs[kMaxJobs];
 };
 
@@ -126,22 +142,9 @@ __device__ __forceinline__ bool view_advance(const UmmaQuantBatch& b, int tile, 
 }
 
 // ---------------------------------------------------------------- epilogue
-// One thread owns one vector.  BITS is a compile-time constant so that the
-// search and the packing unroll completely.
-// Generic (binary search) epilogue for code widths without a search shortcut.  A thread
+// One thread owns one vector (registers = coordinates).
+// Generic (binary search) quantise sweep for codebooks without a search shortcut.  A thread
 // owns all 128 coordinates of one vector; tmem_acc points at its first column.
-__device__ __forceinline__ float ssq_row_generic(uint32_t tmem_acc) {
-  float ssq = 0.f;
-#pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
-    float v[32];
-    tmem_ld32(tmem_acc + c * 32, v);
-#pragma unroll
-    for (int e = 0; e < 32; ++e) ssq = fmaf(v[e], v[e], ssq);
-  }
-  return ssq;
-}
-
 template <int BITS>
 __device__ __forceinline__ void quant_row_generic(uint32_t tmem_acc, float inv, const float* thr, uint8_t* idx_half,
                                                   bool valid) {
@@ -183,6 +186,22 @@ __device__ __forceinline__ void quant_row_generic(uint32_t tmem_acc, float inv, 
   }
 }
 
+// Codebooks without a verified shortcut (none of the Lloyd-Max codebooks): out of line, so that its
+// registers and code do not weigh on the paths that run.
+__device__ __noinline__ void quant_row_search(int bits, uint32_t tacc, float inv, const float* thr, uint8_t* idx_row,
+                                              bool valid) {
+  switch (bits) {
+    case 1: quant_row_generic<1>(tacc, inv, thr, idx_row, valid); break;
+    case 2: quant_row_generic<2>(tacc, inv, thr, idx_row, valid); break;
+    case 3: quant_row_generic<3>(tacc, inv, thr, idx_row, valid); break;
+    case 4: quant_row_generic<4>(tacc, inv, thr, idx_row, valid); break;
+    case 5: quant_row_generic<5>(tacc, inv, thr, idx_row, valid); break;
+    case 6: quant_row_generic<6>(tacc, inv, thr, idx_row, valid); break;
+    case 7: quant_row_generic<7>(tacc, inv, thr, idx_row, valid); break;
+    default: quant_row_generic<8>(tacc, inv, thr, idx_row, valid); break;
+  }
+}
+
 // Search shortcut (see the codebook block): one cubic, one lane look-up of the candidate
 // threshold, one compare.  Arithmetic is kept on the FMA pipe: the index is built as a
 // float next to 2^23 and shifted into the packed word by an integer multiply-add; the
@@ -195,9 +214,13 @@ struct Shortcut {
 
 // CH coordinates (16 here) per step: the loop body stays small enough to live in the
 // instruction cache while four warps per scheduler run it out of phase.
-template <int BITS, int CH, bool NOSHFL = false, bool LINEAR = false>
+// LDS: the candidate's threshold comes from a shared-memory table (thresholds times 2^40) instead of a
+// lane look-up: codes with more than 31 thresholds whose cubic still brackets the index (6 bits).
+// thr_addr is the table's shared address minus 4 * 0x4B000000, so that the look-up address is one
+// multiply-add on the bit pattern of u = 2^23 + e.
+template <int BITS, int CH, bool LDS = false, bool LINEAR = false>
 __device__ __forceinline__ void quant_chunk_fast(const uint32_t (&raw)[CH], const Shortcut& sc, uint8_t* dst,
-                                                 bool valid) {
+                                                 bool valid, uint32_t thr_addr = 0u) {
   constexpr int IPB = 8 / BITS;
   constexpr int BYTES = CH / IPB;               // packed bytes for CH coordinates
   constexpr int WORDS = BYTES >= 4 ? BYTES / 4 : 1;
@@ -222,7 +245,12 @@ __device__ __forceinline__ void quant_chunk_fast(const uint32_t (&raw)[CH], cons
       q = fmaf(q, t, sc.c1);
       u = fmaf(q, t, 8388608.0f);
     }
-    const float thr_h = NOSHFL ? sc.thr_lane_h : __shfl_sync(0xffffffffu, sc.thr_lane_h, __float_as_int(u));
+    float thr_h;
+    if constexpr (LDS) {
+      asm("ld.shared.f32 %0, [%1];" : "=f"(thr_h) : "r"(__float_as_uint(u) * 4u + thr_addr));
+    } else {
+      thr_h = __shfl_sync(0xffffffffu, sc.thr_lane_h, __float_as_int(u));
+    }
     asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(pf) : "f"(r), "f"(sc.h_inv), "f"(-thr_h));
     const float ui = u + pf;
     const int byte = e / IPB;
@@ -279,58 +307,80 @@ __device__ __forceinline__ float ssq_row_fast(uint32_t tacc, uint32_t (&a)[16], 
   return ssq;       // step 0 is in flight into `a`
 }
 
-template <int BITS, bool NOSHFL = false, bool LINEAR = false>
+template <int BITS, bool LDS = false, bool LINEAR = false>
 __device__ __forceinline__ void quant_row_fast(uint32_t tacc, uint32_t (&a)[16], uint32_t (&b)[16], const Shortcut& sc,
-                                               uint8_t* idx_row, bool valid) {
+                                               uint8_t* idx_row, bool valid, uint32_t thr_addr = 0u) {
   constexpr int BYTES = 16 / (8 / BITS);
 #pragma unroll 1
   for (int c = 0; c < 8; c += 2) {
     tmem_wait16(a); tmem_issue16(tacc + (c + 1) * 16, b);
-    quant_chunk_fast<BITS, 16, NOSHFL, LINEAR>(a, sc, idx_row + c * BYTES, valid);
+    quant_chunk_fast<BITS, 16, LDS, LINEAR>(a, sc, idx_row + c * BYTES, valid, thr_addr);
     tmem_wait16(b);
     if (c + 2 < 8) tmem_issue16(tacc + (c + 2) * 16, a);
-    quant_chunk_fast<BITS, 16, NOSHFL, LINEAR>(b, sc, idx_row + (c + 1) * BYTES, valid);
+    quant_chunk_fast<BITS, 16, LDS, LINEAR>(b, sc, idx_row + (c + 1) * BYTES, valid, thr_addr);
   }
 }
 
-// Wide codes (one index per byte): the lower candidate comes from the cell table, then the
-// same saturating-fma compare against that candidate's threshold (stored times 2^40).
-__device__ __forceinline__ void quant_chunk_cells(const uint32_t (&raw)[16], const Shortcut& sc, const float* thr_h,
-                                                  const uint8_t* cells, uint8_t* dst, bool valid) {
+// 7- and 8-bit codes (one index per byte): the candidate e comes from a byte table over the 1024 uniform
+// cells of t, its threshold (times 2^40) from a second table, then the saturating-fma compare.  Random
+// look-ups by 32 lanes cost a shared-memory wavefront per bank collision, and these two were the whole
+// cost of the wide codes, so both tables are stored 16 times and lane l reads copy l / 2: a threshold
+// look-up can only collide inside a lane pair, a cell look-up inside a group of eight lanes.
+// cells_lane = table + lane / 2 - 16 * 0x4B000000 (mod 2^32), so that the cell address is one multiply-add
+// on the bit pattern of u = 2^23 + cell;  thr_lane = table + 4 * (lane / 2).
+__device__ __forceinline__ void quant_chunk_cells(const uint32_t (&raw)[16], const Shortcut& sc, uint32_t cells_lane,
+                                                  uint32_t thr_lane, uint8_t* dst, bool valid) {
   uint32_t acc[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
   for (int e = 0; e < 16; ++e) {
     const float r = __uint_as_float(raw[e]);
-    float t, pf;
+    float t, pf, thr_h;
+    uint32_t e0;
     asm("fma.rn.sat.f32 %0, %1, %2, 0f3F000000;" : "=f"(t) : "f"(r), "f"(sc.s_inv));
     const float u = fmaf(t, 1024.0f, 8388608.0f);
-    const uint32_t e0 = cells[__float_as_uint(u) & 0x7FFu];
-    const float th = thr_h[e0];
-    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(pf) : "f"(r), "f"(sc.h_inv), "f"(-th));
-    const uint32_t idx = e0 + (pf > 0.5f ? 1u : 0u);
-    acc[e >> 2] |= idx << (8 * (e & 3));
+    asm("ld.shared.u8 %0, [%1];" : "=r"(e0) : "r"(__float_as_uint(u) * 16u + cells_lane));
+    asm("ld.shared.f32 %0, [%1];" : "=f"(thr_h) : "r"(e0 * 64u + thr_lane));
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(pf) : "f"(r), "f"(sc.h_inv), "f"(-thr_h));
+    const uint32_t idx = e0 + (__float_as_uint(pf) >> 29);          // pf is 1.0f (0x3F800000) or 0.0f
+    acc[e >> 2] = idx * (1u << (8 * (e & 3))) + acc[e >> 2];
   }
   if (valid) *reinterpret_cast<uint4*>(dst) = make_uint4(acc[0], acc[1], acc[2], acc[3]);
 }
 
 __device__ __forceinline__ void quant_row_cells(uint32_t tacc, uint32_t (&a)[16], uint32_t (&b)[16], const Shortcut& sc,
-                                                const float* thr_h, const uint8_t* cells, uint8_t* idx_row, bool valid) {
+                                                uint32_t cells_lane, uint32_t thr_lane, uint8_t* idx_row, bool valid) {
 #pragma unroll 1
   for (int c = 0; c < 8; c += 2) {
     tmem_wait16(a); tmem_issue16(tacc + (c + 1) * 16, b);
-    quant_chunk_cells(a, sc, thr_h, cells, idx_row + c * 16, valid);
+    quant_chunk_cells(a, sc, cells_lane, thr_lane, idx_row + c * 16, valid);
     tmem_wait16(b);
     if (c + 2 < 8) tmem_issue16(tacc + (c + 2) * 16, a);
-    quant_chunk_cells(b, sc, thr_h, cells, idx_row + (c + 1) * 16, valid);
+    quant_chunk_cells(b, sc, cells_lane, thr_lane, idx_row + (c + 1) * 16, valid);
   }
 }
 
-template <bool BF16>
+// Rest of a role's walk after one of its waits ran out: only the two named barriers of every job
+// change, so that the other warps of the group never wait for this one.  Out of line: cold.
+__device__ __noinline__ void walk_job_barriers(const UmmaQuantBatch& batch, int job_index, int t0, int i, int step,
+                                               int n_local, int bar_id, int threads) {
+  QuantJobView job;
+  job.j = job_index;
+  job.end = (job_index + 1 < batch.n_jobs) ? batch.jobs[job_index + 1].tile_begin : batch.total_tiles;
+  for (i += step; i < n_local; i += step)
+    if (view_advance(batch, t0 + i, job)) {
+      asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(threads) : "memory");
+      asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(threads) : "memory");
+    }
+}
+
+// WIDE: the launch holds a job with codes of 6 bits or more; the narrow instantiation carries none of
+// the wide-code paths (its epilogue loop is sensitive to code size).
+template <bool BF16, bool WIDE>
 __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_constant__ UmmaQuantBatch batch) {
-  constexpr int kStages = Cfg<BF16>::kStages;
-  constexpr int kPieces = Cfg<BF16>::kPieces;
-  constexpr uint32_t kOffA = Cfg<BF16>::kOffA, kOffPi = Cfg<BF16>::kOffPi, kOffThr = Cfg<BF16>::kOffThr,
-                     kOffBar = Cfg<BF16>::kOffBar;
+  using C = Cfg<BF16, WIDE>;
+  constexpr int kStages = C::kStages;
+  constexpr int kPieces = C::kPieces;
+  constexpr uint32_t kOffA = C::kOffA, kOffPi = C::kOffPi, kOffThr = C::kOffThr, kOffBar = C::kOffBar;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
@@ -349,9 +399,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + kOffBar + 208);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total = batch.total_tiles;
-  const int t0 = (int)((int64_t)total * blockIdx.x / gridDim.x);
-  const int t1 = (int)((int64_t)total * (blockIdx.x + 1) / gridDim.x);
+  const int t0 = batch.cta_begin[blockIdx.x];
+  const int t1 = batch.cta_begin[blockIdx.x + 1];
   const int n_local = t1 - t0;
 
   if (threadIdx.x == 0) {
@@ -380,7 +429,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
           if (pi_loads > 0) ok = mbar_wait(bar_pifree, (uint32_t)((pi_loads - 1) & 1), abort_flag);
           if (!ok) break;
           mbar_arrive_expect_tx(bar_pifull, kPieces * kTileBytes);
-          const uint8_t* img = reinterpret_cast<const uint8_t*>(job.image) + Cfg<BF16>::kPieceOff;
+          const uint8_t* img = reinterpret_cast<const uint8_t*>(job.image) + C::kPieceOff;
 #pragma unroll
           for (int p = 0; p < kPieces; ++p) bulk_load(pi_smem + p * kTileBytes, img + p * kTileBytes, kTileBytes, bar_pifull);
           ++pi_loads;
@@ -395,9 +444,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
         const int slab = lt / job.tps;
         const int row0 = (lt - slab * job.tps) * kTileRows;
         const int bb = slab / job.H, hh = slab - bb * job.H;
-        if (batch.ablate & 64) {
+        if (TQ_ABL(batch, 64)) {
           mbar_arrive(bar_full + 8 * s);
-        } else if (batch.ablate & 32) {
+        } else if (TQ_ABL(batch, 32)) {
           mbar_arrive_expect_tx(bar_full + 8 * s, kHalfBytes);
           tma_load_4d(a_smem + s * kTileBytes, job.tmap, 0, row0, hh, bb, bar_full + 8 * s);
         } else {
@@ -447,22 +496,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
         const uint64_t a_base = smem_desc_sw128(a_smem + s * kTileBytes);
         const bool last_of_job = i + 1 >= n_local || t + 1 >= job.end;
         if (elect_one()) {
-          if (batch.ablate & 8192) {
-            // timing only: the same work as 32 MMAs of N = 64 (two column halves)
-            const uint32_t idesc64 = (idesc & ~(0x3Fu << 17)) | ((64u >> 3) << 17);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-#pragma unroll
-              for (int piece = 0; piece < kPieces; ++piece) {
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                  const uint64_t koff = (uint64_t)(((k >> 2) * kHalfBytes + (k & 3) * 32) / 16);
-                  const uint64_t poff = (uint64_t)((piece * kTileBytes + h * 8192) / 16);
-                  umma_f16(d_tmem + (uint32_t)(h * 64), a_base + koff, b_base + poff + koff, idesc64, (piece | k) != 0 ? 1u : 0u);
-                }
-              }
-            }
-          } else if (!(batch.ablate & 4)) {
+          if (!TQ_ABL(batch, 4)) {
 #pragma unroll
             for (int piece = 0; piece < kPieces; ++piece) {
 #pragma unroll
@@ -474,7 +508,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
               }
             }
           }
-          if (batch.ablate & 128) mbar_arrive(bar_tfull + 8 * b); else
           umma_commit(bar_tfull + 8 * b);      // one commit per tile: the epilogue and the producer both wait on it
           if (last_of_job) umma_commit(bar_pifree);
         }
@@ -487,70 +520,109 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
     }
   } else {
     // ------------------------------------------------------------ epilogue warpgroups
+    // `ok` is made warp-uniform after each wait because the TMEM loads are warp-collective.  A warp
+    // whose wait ran out leaves the working loop and walks the rest of its tiles for the named
+    // barriers of the job changes alone, so that the other warps of the group never wait for it.
     const int ew = warp - 2;
     const int wg = ew >> 2;                    // 0..3, also the accumulator this group reads
     const int quarter = warp & 3;              // TMEM lanes this warp may touch: 32*quarter ..
     const int row = quarter * 32 + lane;
-    float* thr = thr_all + wg * (Cfg<BF16>::kThrRegion / 4);
-    uint8_t* cells = reinterpret_cast<uint8_t*>(thr + 256);
+    float* thr = thr_all + wg * (C::kThrRegion / 4);                            // narrow launches: per warpgroup
     const int wg_tid = (ew & 3) * 32 + lane;
+    const int ep_tid = threadIdx.x - 64;                                        // 0..511 over the epilogue warps
     int mode = 0;                               // 0 search, 1 cubic shortcut, 2 cell table
     bool ok = true;
-    bool fast = false, linear = false;
+    bool fast = false, fast_lds = false, linear = false;
     Shortcut sc = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     QuantJobView job;
-    for (int i = wg; i < n_local && ok; i += 4) {
+    // Wide launches keep ONE set of tables per CTA.  Every epilogue warp walks the CTA's jobs in order,
+    // one at a time: barrier (all warpgroups are done with the previous job's tables), rebuild, barrier.
+    // All sixteen warps pass the same sequence of barriers whatever tiles they own, also after a wait ran
+    // out and after their last tile, so nobody waits for a warp that has left.
+    int seq_job = 0, last_job = -1;
+    if constexpr (WIDE) {
+      while (seq_job + 1 < batch.n_jobs && t0 >= batch.jobs[seq_job + 1].tile_begin) ++seq_job;
+      last_job = seq_job;
+      while (last_job + 1 < batch.n_jobs && t1 - 1 >= batch.jobs[last_job + 1].tile_begin) ++last_job;
+      if (n_local <= 0) last_job = seq_job - 1;
+      --seq_job;                                // nothing built yet
+    }
+    auto build_tables_up_to = [&](int target) {
+      while (seq_job < target) {
+        ++seq_job;
+        asm volatile("bar.sync 5, 512;" ::: "memory");
+        const float* cb = batch.jobs[seq_job].codebook;
+        const int jbits = batch.jobs[seq_job].bits;
+        const int jmode = (int)__ldg(cb + 512);
+        if (jmode == 2 && jbits >= 5) {
+          float* thr_rep = reinterpret_cast<float*>(gbase + C::kOffThr);        // [256][16]
+          for (int k = ep_tid; k < 256 * 16; k += 512) thr_rep[k] = __ldg(cb + kThresholdOff + (k >> 4)) * 1099511627776.0f;
+          const uint8_t* cell_e = reinterpret_cast<const uint8_t*>(cb + 528);
+          uint32_t* cells_rep = reinterpret_cast<uint32_t*>(gbase + C::kOffCells);   // [1025][16 bytes]
+          for (int k = ep_tid; k < 1025 * 4; k += 512) cells_rep[k] = (uint32_t)__ldg(cell_e + (k >> 2)) * 0x01010101u;
+        } else if (jmode == 1 && jbits == 6) {
+          float* thr6 = reinterpret_cast<float*>(gbase + C::kOffThr6);
+          if (ep_tid < 64) thr6[ep_tid] = __ldg(cb + kThresholdOff + ep_tid) * 1099511627776.0f;
+        }
+        asm volatile("bar.sync 5, 512;" ::: "memory");
+      }
+    };
+    int i = wg;
+    for (; i < n_local; i += 4) {
       const int t = t0 + i;
       if (view_advance(batch, t, job)) {
-        asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");     // previous tile's readers are done
-        mode = (int)__ldg(job.codebook + 512);
-        if (mode == 2 && job.bits < 5) mode = 0;
-        const float tscale = mode == 2 ? 1099511627776.0f : 1.0f;      // the cell path compares against thr * 2^40
-        thr[wg_tid] = __ldg(job.codebook + kThresholdOff + wg_tid) * tscale;
-        thr[wg_tid + 128] = __ldg(job.codebook + kThresholdOff + 128 + wg_tid) * tscale;
-        if (mode == 2)
-          for (int e = wg_tid; e < 257; e += 128)
-            reinterpret_cast<uint32_t*>(cells)[e] = __float_as_uint(__ldg(job.codebook + 528 + e));
-        fast = mode == 1 && job.bits <= 5;
+        if constexpr (WIDE) {
+          build_tables_up_to(job.j);
+          mode = (int)__ldg(job.codebook + 512);
+          fast = mode == 1 && job.bits <= 5;        // up to 31 thresholds: one per lane
+          fast_lds = mode == 1 && job.bits == 6;    // 63 thresholds: the candidate's threshold comes from shared memory
+          if ((mode == 2 && job.bits < 5) || (mode == 1 && job.bits > 6)) mode = 0;
+        } else {
+          asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");     // previous tile's readers are done
+          mode = (int)__ldg(job.codebook + 512);
+          fast = mode == 1 && job.bits <= 5;
+          if (!fast) mode = 0;
+          thr[wg_tid] = __ldg(job.codebook + kThresholdOff + wg_tid);
+          thr[wg_tid + 128] = __ldg(job.codebook + kThresholdOff + 128 + wg_tid);
+        }
         linear = __ldg(job.codebook + 518) == 1.0f;
         sc.s = __ldg(job.codebook + 513);
         sc.c1 = __ldg(job.codebook + 514);
         sc.c2 = __ldg(job.codebook + 515);
         sc.c3 = __ldg(job.codebook + 516);
         sc.thr_lane_h = __ldg(job.codebook + kThresholdOff + lane) * 1099511627776.0f;
-        asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");
+        if constexpr (!WIDE) asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");
       }
-      ok = mbar_wait(bar_tfull + 8 * wg, (uint32_t)((i / kAccBufs) & 1), abort_flag);
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * wg, (uint32_t)((i / kAccBufs) & 1), abort_flag));
       if (!ok) break;
       tc_fence_after();
       const int lt = t - job.begin;
       const int slab = lt / job.tps;
       const int64_t s_row = (int64_t)(lt - slab * job.tps) * kTileRows + row;
-      const bool valid = s_row < job.S && !(batch.ablate & 1);
+      const bool valid = s_row < job.S && !TQ_ABL(batch, 1);
       const int64_t n = (int64_t)slab * job.S + s_row;
       const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(wg * 128);
       uint8_t* idx_row = job.idx_out + n * (int64_t)job.g;
-      if (!(batch.ablate & 2)) {
+      if (!TQ_ABL(batch, 2)) {
         uint32_t ra[16], rb[16];
         float ssq;
-        if (batch.ablate & 512) { ssq = 1.0f; if (fast || mode == 2) tmem_issue16(tacc, ra); }
-        else ssq = (fast || mode == 2) ? ssq_row_fast(tacc, ra, rb) : ssq_row_generic(tacc);
+        if (TQ_ABL(batch, 512)) { ssq = 1.0f; tmem_issue16(tacc, ra); }
+        else ssq = ssq_row_fast(tacc, ra, rb);
         const float norm = __fsqrt_rn(ssq);
         const float inv = __fdiv_rn(1.0f, norm + 1e-8f);
         if (valid) job.norms_out[n] = __half_as_ushort(__float2half_rn(norm));
-        if (batch.ablate & 256) {
-          if (fast || mode == 2) tmem_wait16(ra);
-        } else if (mode == 2) {
-          sc.s_inv = sc.s * inv;
-          sc.h_inv = 1099511627776.0f * inv;
-          quant_row_cells(tacc, ra, rb, sc, thr, cells, idx_row, valid);
+        sc.s_inv = sc.s * inv;
+        sc.h_inv = 1099511627776.0f * inv;            // 2^40: exact scaling
+        if (TQ_ABL(batch, 256)) {
+          tmem_wait16(ra);
+        } else if (WIDE && mode == 2) {
+          if constexpr (WIDE)
+            quant_row_cells(tacc, ra, rb, sc, base + C::kOffCells + (uint32_t)(lane >> 1) - 16u * 0x4B000000u,
+                            base + C::kOffThr + 4u * (uint32_t)(lane >> 1), idx_row, valid);
+        } else if (WIDE && fast_lds) {
+          if constexpr (WIDE)
+            quant_row_fast<6, true>(tacc, ra, rb, sc, idx_row, valid, base + C::kOffThr6 - 4u * 0x4B000000u);
         } else if (fast) {
-          sc.s_inv = sc.s * inv;
-          sc.h_inv = 1099511627776.0f * inv;          // 2^40: exact scaling
-          if (batch.ablate & 16) {
-            if (job.bits == 4) quant_row_fast<4, true>(tacc, ra, rb, sc, idx_row, valid);
-            else quant_row_fast<2, true>(tacc, ra, rb, sc, idx_row, valid);
-          } else
           switch (job.bits) {
             case 1:
               if (linear) quant_row_fast<1, false, true>(tacc, ra, rb, sc, idx_row, valid);
@@ -568,16 +640,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
             default: quant_row_fast<5>(tacc, ra, rb, sc, idx_row, valid); break;
           }
         } else {
-          switch (job.bits) {
-            case 1: quant_row_generic<1>(tacc, inv, thr, idx_row, valid); break;
-            case 2: quant_row_generic<2>(tacc, inv, thr, idx_row, valid); break;
-            case 3: quant_row_generic<3>(tacc, inv, thr, idx_row, valid); break;
-            case 4: quant_row_generic<4>(tacc, inv, thr, idx_row, valid); break;
-            case 5: quant_row_generic<5>(tacc, inv, thr, idx_row, valid); break;
-            case 6: quant_row_generic<6>(tacc, inv, thr, idx_row, valid); break;
-            case 7: quant_row_generic<7>(tacc, inv, thr, idx_row, valid); break;
-            default: quant_row_generic<8>(tacc, inv, thr, idx_row, valid); break;
-          }
+          tmem_wait16(ra);                       // the norm sweep left a load in flight
+          // wide launches have no plain threshold table in shared memory: the search reads the codebook block
+          quant_row_search(job.bits, tacc, inv, WIDE ? job.codebook + kThresholdOff : thr, idx_row, valid);
         }
       }
       tc_fence_before();
@@ -587,6 +652,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
     if (!ok && lane == 0) {
       *abort_flag = 1;
       if (batch.status != nullptr) atomicCAS(batch.status, 0, (3 << 16) | (int)blockIdx.x);
+    }
+    if constexpr (WIDE) {
+      build_tables_up_to(last_job);              // the rest of the CTA's job sequence: barriers for the others
+    } else {
+      if (!ok) walk_job_barriers(batch, job.j, t0, i, 4, n_local, wg + 1, 128);
     }
   }
   tc_fence_before();
@@ -626,8 +696,9 @@ struct UmmaDeqBatch {
   int32_t n_jobs;
   int32_t total_tiles;
   int32_t* status;
-  int32_t ablate;            // timing experiments only (TQ_ABLATE): 1 skip stores, 2 skip expansion, 4 skip MMA
+  int32_t ablate;            // -DTQ_ABLATION builds only (TQ_ABLATE): 1 skip stores, 2 skip expansion, 4 skip MMA, 8 skip the drain arithmetic
   int32_t pad_[3];
+  int32_t cta_begin[kMaxCtas + 1];   // tiles [cta_begin[c], cta_begin[c + 1]) belong to CTA c (equal estimated cost)
   UmmaDeqJob jobs[kMaxDeqJobs];
 };
 static_assert(sizeof(UmmaDeqBatch) < 32000, "kernel parameter space");
@@ -652,7 +723,10 @@ struct DCfg {
   static constexpr uint32_t kOffPi = kOffA + kNA * kPiecesA * kTileBytes;
   static constexpr uint32_t kOffPk = kOffPi + kPiecesB * kTileBytes;
   static constexpr uint32_t kOffStage = kOffPk + kPk * kPkBytes;           // 16-bit outputs: one tile per drain group
-  static constexpr uint32_t kOffBar = kOffStage + (OUT32 ? 0u : 2u * kTileBytes);
+  // 16-bit outputs of wide codes: replicated fp16 look-up table, 256 entries x 32 copies x 2 bytes
+  static constexpr bool kWide16 = !OUT32 && !NARROW;
+  static constexpr uint32_t kOffLut16 = kOffStage + (OUT32 ? 0u : 2u * kTileBytes);
+  static constexpr uint32_t kOffBar = kOffLut16 + (kWide16 ? 16384u : 0u);
   static constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;
 };
 // + 1 KB of static shared memory for the centroid look-up table
@@ -805,9 +879,8 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + C::kOffBar + 208);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total = batch.total_tiles;
-  const int t0 = (int)((int64_t)total * blockIdx.x / gridDim.x);
-  const int t1 = (int)((int64_t)total * (blockIdx.x + 1) / gridDim.x);
+  const int t0 = batch.cta_begin[blockIdx.x];
+  const int t1 = batch.cta_begin[blockIdx.x + 1];
   const int n_local = t1 - t0;
 
   if (threadIdx.x == 0) {
@@ -889,7 +962,7 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
         const uint64_t a_base = smem_desc_sw128(a_smem + a * C::kPiecesA * kTileBytes);
         const uint64_t b_base = smem_desc_sw128(pi_smem);
         constexpr int kPasses = OUT32 ? 3 : 1;      // hi.hi [, lo.hi, hi.lo]
-        if (!(batch.ablate & 4)) {
+        if (!TQ_ABL(batch, 4)) {
 #pragma unroll
           for (int pass = 0; pass < kPasses; ++pass) {
 #pragma unroll
@@ -911,12 +984,15 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
       }
     }
   } else if (warp < 2 + C::kExpWarps) {
-    // ---- expanders: 256 threads, one half row each
+    // ---- expanders: 256 threads, one half row each.  A warp whose wait ran out leaves the working
+    // loop and walks on for the job-change barriers alone (see the quantize epilogue).
     const int et = threadIdx.x - 64;             // 0..255
     const int row = et & 127, half = et >> 7;   // a quarter warp = 8 rows of one k-half: conflict-free operand stores
+    const uint32_t lut16_lane = base + C::kOffLut16 + 2u * (uint32_t)lane;
     bool ok = true;
     DeqJobView job;
-    for (int i = 0; i < n_local && ok; ++i) {
+    int i = 0;
+    for (; i < n_local; ++i) {
       const int t = t0 + i;
       if (view_advance(batch, t, job)) {
         asm volatile("bar.sync 1, 256;" ::: "memory");       // everyone is past the previous tile's look-ups
@@ -924,20 +1000,28 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
         const __half h = __float2half_rn(c);
         const __half l = __float2half_rn(c - __half2float(h));
         lut[et] = (uint32_t)__half_as_ushort(h) | ((uint32_t)__half_as_ushort(l) << 16);
+        if constexpr (C::kWide16) {
+          if (job.bits >= 5) {                  // 32 copies of entry `et`, two per 32-bit store
+            const uint32_t hh = (uint32_t)__half_as_ushort(h) * 0x00010001u;
+            uint32_t* copies = reinterpret_cast<uint32_t*>(gbase + C::kOffLut16) + et * 16;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) copies[k] = hh;
+          }
+        }
         asm volatile("bar.sync 1, 256;" ::: "memory");
       }
       const int s = i % kPk, a = i % kNA;
       ok = mbar_wait(bar_pkfull + 8 * s, (uint32_t)((i / kPk) & 1), abort_flag);
-      if (!ok) break;
-      if (i >= kNA) {           // the operand stage is free once the MMAs of tile i - kNA are done
+      if (ok && i >= kNA) {     // the operand stage is free once the MMAs of tile i - kNA are done
         const int d = i - kNA;
         ok = mbar_wait(bar_tfull + 8 * (d % kNT), (uint32_t)((d / kNT) & 1), abort_flag);
-        if (!ok) break;
       }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       const int lt = t - job.begin;
       const int slab = lt / job.tps;
       const int64_t s_row = (int64_t)(lt - slab * job.tps) * kTileRows + row;
-      if (s_row < job.S && !(batch.ablate & 2)) {
+      if (s_row < job.S && !TQ_ABL(batch, 2)) {
         const int g = job.g;
         const uint32_t src = pk_smem + s * C::kPkBytes + (uint32_t)(row * g + half * (g >> 1));
         const uint32_t a_stage = a_smem + a * C::kPiecesA * kTileBytes;
@@ -946,22 +1030,42 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
           case 2: expand_half<2, C::kPiecesA>(src, lut, a_stage, row, half); break;
           case 3: expand_half<3, C::kPiecesA>(src, lut, a_stage, row, half); break;
           case 4: expand_half<4, C::kPiecesA>(src, lut, a_stage, row, half); break;
-          case 5: expand_half<5, C::kPiecesA>(src, lut, a_stage, row, half); break;
-          case 6: expand_half<6, C::kPiecesA>(src, lut, a_stage, row, half); break;
-          case 7: expand_half<7, C::kPiecesA>(src, lut, a_stage, row, half); break;
-          default: expand_half<8, C::kPiecesA>(src, lut, a_stage, row, half); break;
+          case 5:
+            if constexpr (C::kWide16) expand_half_wide16<5>(src, lut16_lane, a_stage, row, half);
+            else expand_half<5, C::kPiecesA>(src, lut, a_stage, row, half);
+            break;
+          case 6:
+            if constexpr (C::kWide16) expand_half_wide16<6>(src, lut16_lane, a_stage, row, half);
+            else expand_half<6, C::kPiecesA>(src, lut, a_stage, row, half);
+            break;
+          case 7:
+            if constexpr (C::kWide16) expand_half_wide16<7>(src, lut16_lane, a_stage, row, half);
+            else expand_half<7, C::kPiecesA>(src, lut, a_stage, row, half);
+            break;
+          default:
+            if constexpr (C::kWide16) expand_half_wide16<8>(src, lut16_lane, a_stage, row, half);
+            else expand_half<8, C::kPiecesA>(src, lut, a_stage, row, half);
+            break;
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // operand writes -> visible to the tensor core
       mbar_arrive(bar_afull + 8 * a);
       mbar_arrive(bar_pkempty + 8 * s);
     }
-    if (!ok && lane == 0) {
-      *abort_flag = 1;
-      if (batch.status != nullptr) atomicCAS(batch.status, 0, (6 << 16) | (int)blockIdx.x);
+    if (!ok) {
+      if (lane == 0) {
+        *abort_flag = 1;
+        if (batch.status != nullptr) atomicCAS(batch.status, 0, (6 << 16) | (int)blockIdx.x);
+      }
+      for (++i; i < n_local; ++i)
+        if (view_advance(batch, t0 + i, job)) {
+          asm volatile("bar.sync 1, 256;" ::: "memory");
+          asm volatile("bar.sync 1, 256;" ::: "memory");
+        }
     }
   } else {
-    // ---- drain: two warpgroups, alternate tiles
+    // ---- drain: two warpgroups, alternate tiles.  `ok` is warp-uniform; a warp whose wait ran out
+    // leaves the working loop and still passes the two named barriers of every remaining tile of its group.
     const int dw = warp - (2 + C::kExpWarps);    // 0..7
     const int wg = dw >> 2;
     const int quarter = warp & 3;
@@ -970,7 +1074,8 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
     const uint32_t stage = base + C::kOffStage + (uint32_t)wg * kTileBytes;
     bool ok = true;
     DeqJobView job;
-    for (int i = wg; i < n_local && ok; i += 2) {
+    int i = wg;
+    for (; i < n_local; i += 2) {
       const int t = t0 + i;
       view_advance(batch, t, job);
       const int lt = t - job.begin;
@@ -982,7 +1087,7 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
       const float nv = valid ? __half2float(__ushort_as_half(__ldg(job.norms + n))) : 0.f;   // in flight during the wait
       const int bb = slab / job.H, hh = slab - bb * job.H;
       const int b = i % kNT;
-      ok = mbar_wait(bar_tfull + 8 * b, (uint32_t)((i / kNT) & 1), abort_flag);
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * b, (uint32_t)((i / kNT) & 1), abort_flag));
       if (!ok) break;
       tc_fence_after();
       const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * 128);
@@ -996,20 +1101,28 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
         // the previous tile's store must have finished reading the staging tile
         if (wg_tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         asm volatile("bar.sync %0, 128;" ::"r"(wg + 2) : "memory");
-        if (batch.ablate & 8) {
+        if (TQ_ABL(batch, 8)) {
         } else if (job.out_dtype == TQ_F16) drain_row_staged<TQ_F16>(tacc, nv, stage, row);
         else drain_row_staged<TQ_BF16>(tacc, nv, stage, row);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_tempty + 8 * b);               // the accumulator is free again
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staging writes -> visible to the TMA engine
-        asm volatile("bar.sync %0, 128;" ::"r"(wg + 2) : "memory");
-        if (wg_tid == 0 && !(batch.ablate & 1)) {
+        // the tile is stored only if every warp of the group drained its rows
+        const bool all_ok = bar_red_and(wg + 2, 128, true);
+        if (wg_tid == 0 && all_ok && !TQ_ABL(batch, 1)) {
           tma_store_4d(job.out_map, stage, 0, s0, hh, bb);
           tma_store_4d(job.out_map, stage + kHalfBytes, 64, s0, hh, bb);
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
       }
+    }
+    if constexpr (!OUT32) {
+      if (!ok)                                     // keep the group's two barriers per tile complete
+        for (; i < n_local; i += 2) {
+          asm volatile("bar.sync %0, 128;" ::"r"(wg + 2) : "memory");
+          bar_red_and(wg + 2, 128, false);
+        }
     }
     if constexpr (!OUT32) {
       if (wg_tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all stores done before exit
@@ -1058,8 +1171,48 @@ typedef TensorMapEncodeFn EncodeTiledFn;
 EncodeTiledFn encode_fn() { return tensor_map_encoder(); }
 
 int ablate_flags() {
+#ifdef TQ_ABLATION
   const char* e = getenv("TQ_ABLATE");
   return e != nullptr ? atoi(e) : 0;
+#else
+  return 0;
+#endif
+}
+
+// Contiguous tile ranges of equal estimated cost: job j has tiles[j] tiles that cost weight[j] each.
+// A launch that mixes code widths would otherwise finish with the CTAs that drew the slow tiles.
+void partition_tiles(const int64_t* tiles, const int* weight, int n_jobs, int grid, int32_t* cta_begin) {
+  double total = 0.0;
+  int64_t total_tiles = 0;
+  for (int j = 0; j < n_jobs; ++j) { total += (double)tiles[j] * weight[j]; total_tiles += tiles[j]; }
+  int j = 0;
+  double cum = 0.0;          // cost of the jobs before j
+  int64_t base = 0;          // tiles of the jobs before j
+  cta_begin[0] = 0;
+  for (int c = 1; c < grid; ++c) {
+    const double target = total * c / grid;
+    while (j < n_jobs && cum + (double)tiles[j] * weight[j] <= target) {
+      cum += (double)tiles[j] * weight[j];
+      base += tiles[j];
+      ++j;
+    }
+    int64_t b = j >= n_jobs ? total_tiles : base + (int64_t)((target - cum) / weight[j]);
+    if (b > total_tiles) b = total_tiles;
+    if (b < cta_begin[c - 1]) b = cta_begin[c - 1];
+    cta_begin[c] = (int32_t)b;
+  }
+  cta_begin[grid] = (int32_t)total_tiles;
+}
+
+// Cost of a 128-vector tile per code width, in units of 10 ns on one SM at full clocks (measured on
+// (8, 8, 32768, 128) tensors, one width at a time); only the ratios matter.
+int quantize_tile_weight(int bits, bool bf16) {
+  if (bf16) return bits <= 2 ? 142 : bits <= 4 ? 153 : bits == 5 ? 159 : bits == 6 ? 200 : 289;
+  return bits <= 2 ? 120 : bits <= 4 ? 139 : bits == 5 ? 172 : bits == 6 ? 195 : 288;
+}
+int dequantize_tile_weight(int bits, bool out32) {
+  if (out32) return bits <= 4 ? 250 : 300;
+  return bits <= 2 ? 128 : bits <= 4 ? 140 : 211;
 }
 
 }  // namespace
@@ -1127,10 +1280,14 @@ int umma_quantize(const TqQuantizeJob* jobs, int n_jobs, cudaStream_t st) {
   while (done < n_jobs) {
     const int take = (n_jobs - done) < kMaxJobs ? (n_jobs - done) : kMaxJobs;
     int64_t tile_cursor = 0;
+    int64_t job_tiles[kMaxJobs];
+    int job_weight[kMaxJobs];
     for (int i = 0; i < take && !reuse; ++i) {
       const TqQuantizeJob& j = jobs[done + i];
       UmmaQuantJob& u = batch.jobs[i];
       const int64_t tps = (j.S + kTileRows - 1) / kTileRows;
+      job_tiles[i] = tps * j.B * j.H;
+      job_weight[i] = quantize_tile_weight(j.bits, j.x_dtype == TQ_BF16);
       // size-1 dimensions get a harmless stride; TMA wants multiples of 16 bytes
       const int64_t ss = j.S > 1 ? j.stride_s : kDim;
       const int64_t sh = j.H > 1 ? j.stride_h : ss * j.S;
@@ -1159,7 +1316,10 @@ int umma_quantize(const TqQuantizeJob* jobs, int n_jobs, cudaStream_t st) {
     }
     int grid = last_grid;
     const bool bf16 = jobs[done].x_dtype == TQ_BF16;
-    const uint32_t smem = bf16 ? Cfg<true>::kSmemBytes : Cfg<false>::kSmemBytes;
+    bool wide = false;
+    for (int i = 0; i < take; ++i) wide = wide || jobs[done + i].bits > 5;
+    const uint32_t smem = bf16 ? (wide ? Cfg<true, true>::kSmemBytes : Cfg<true, false>::kSmemBytes)
+                               : (wide ? Cfg<false, true>::kSmemBytes : Cfg<false, false>::kSmemBytes);
     if (!reuse) {
       batch.n_jobs = take;
       batch.total_tiles = (int32_t)tile_cursor;
@@ -1169,13 +1329,24 @@ int umma_quantize(const TqQuantizeJob* jobs, int n_jobs, cudaStream_t st) {
       batch.status = reinterpret_cast<int32_t*>(status_ptr);
       int sms = 148;
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, cur_dev);
+      if (sms > kMaxCtas) sms = kMaxCtas;
       grid = (int)(tile_cursor < sms ? tile_cursor : sms);
-      cudaError_t e = bf16 ? cudaFuncSetAttribute(k_umma_quantize<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                           : cudaFuncSetAttribute(k_umma_quantize<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) { note_cuda_error((int)e); return TQ_ELAUNCH; }
+      partition_tiles(job_tiles, job_weight, take, grid, batch.cta_begin);
     }
-    if (bf16) k_umma_quantize<true><<<grid, kThreads, smem, st>>>(batch);
-    else k_umma_quantize<false><<<grid, kThreads, smem, st>>>(batch);
+    auto launch = [&](auto kern) -> int {
+      if (!reuse) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { note_cuda_error((int)e); return TQ_ELAUNCH; }
+      }
+      kern<<<grid, kThreads, smem, st>>>(batch);
+      return TQ_OK;
+    };
+    int lrc;
+    if (bf16 && wide) lrc = launch(k_umma_quantize<true, true>);
+    else if (bf16) lrc = launch(k_umma_quantize<true, false>);
+    else if (wide) lrc = launch(k_umma_quantize<false, true>);
+    else lrc = launch(k_umma_quantize<false, false>);
+    if (lrc != TQ_OK) return lrc;
     int rc = check_launch();
     if (rc != TQ_OK) return rc;
     last_grid = grid;
@@ -1220,10 +1391,14 @@ int umma_dequantize(const TqDequantizeJob* jobs, int n_jobs, cudaStream_t st) {
   while (done < n_jobs) {
     const int take = (n_jobs - done) < kMaxDeqJobs ? (n_jobs - done) : kMaxDeqJobs;
     int64_t tile_cursor = 0;
+    int64_t job_tiles[kMaxDeqJobs];
+    int job_weight[kMaxDeqJobs];
     for (int i = 0; i < take && !reuse; ++i) {
       const TqDequantizeJob& j = jobs[done + i];
       UmmaDeqJob& u = batch.jobs[i];
       const int64_t tps = (j.S + kTileRows - 1) / kTileRows;
+      job_tiles[i] = tps * j.B * j.H;
+      job_weight[i] = dequantize_tile_weight(j.bits, j.out_dtype == TQ_F32);
       if (j.out_dtype != TQ_F32) {
         const int64_t ss = j.S > 1 ? j.ostride_s : kDim;
         const int64_t sh = j.H > 1 ? j.ostride_h : ss * j.S;
@@ -1263,7 +1438,9 @@ int umma_dequantize(const TqDequantizeJob* jobs, int n_jobs, cudaStream_t st) {
       batch.status = reinterpret_cast<int32_t*>(status_ptr);
       int sms = 148;
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, cur_dev);
+      if (sms > kMaxCtas) sms = kMaxCtas;
       grid = (int)(tile_cursor < sms ? tile_cursor : sms);
+      partition_tiles(job_tiles, job_weight, take, grid, batch.cta_begin);
     }
     const bool out32 = jobs[done].out_dtype == TQ_F32;
     bool narrow = true;

@@ -13,7 +13,9 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libturboquant_b200.so")
+# TURBOQUANT_B200_LIB points at another build of the same library (a profiling build made with
+# `build.py --ablate --out ...`); unset, the in-tree library next to this file is loaded.
+LIB_PATH = os.environ.get("TURBOQUANT_B200_LIB") or os.path.join(_HERE, "libturboquant_b200.so")
 
 F32, F16, BF16 = 0, 1, 2
 IDX_PACKED, IDX_U8, IDX_I64 = 0, 1, 2
@@ -41,6 +43,13 @@ class DequantizeJob(C.Structure):
                 ("bits", C.c_int32), ("out_dtype", C.c_int32), ("B", C.c_int64), ("H", C.c_int64), ("S", C.c_int64),
                 ("out", C.c_void_p), ("ostride_b", C.c_int64), ("ostride_h", C.c_int64), ("ostride_s", C.c_int64),
                 ("rotation", C.c_void_p), ("codebook", C.c_void_p), ("rotation_image", C.c_void_p)]
+
+
+class CopyJob(C.Structure):
+    _fields_ = [("src", C.c_void_p), ("dst", C.c_void_p), ("elem_bytes", C.c_int32), ("D", C.c_int32),
+                ("B", C.c_int64), ("H", C.c_int64), ("S", C.c_int64),
+                ("sstride_b", C.c_int64), ("sstride_h", C.c_int64), ("sstride_s", C.c_int64),
+                ("dstride_b", C.c_int64), ("dstride_h", C.c_int64), ("dstride_s", C.c_int64)]
 
 
 class ScoreJob(C.Structure):
@@ -97,6 +106,8 @@ def lib():
     L.tq_quantize.argtypes = [C.POINTER(QuantizeJob), i32, vp]
     L.tq_dequantize.argtypes = [C.POINTER(DequantizeJob), i32, vp]
     L.tq_project.argtypes = [vp, i32, i64, i32, vp, i32, vp, vp]
+    L.tq_copy_rows.argtypes = [C.POINTER(CopyJob), i32, vp]
+    L.tq_ablation_build.restype = i32
     L.tq_score_workspace_bytes.restype = sz
     L.tq_score_workspace_bytes.argtypes = [i64, i64, i64, i64, i32]
     L.tq_score_packed.argtypes = [C.POINTER(ScoreJob), vp]
@@ -109,7 +120,7 @@ def lib():
     L.tq_qjl_scores.argtypes = [C.POINTER(QjlScoreJob), vp]
     L.tq_prod_inner_product.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, vp, vp, vp, vp, sz, vp]
     for name in ("tq_packed_row_bytes", "tq_build_codebook", "tq_quantize_rotated", "tq_quantize", "tq_dequantize",
-                 "tq_project", "tq_score_packed", "tq_score_packed_noalloc", "tq_qjl_compress", "tq_qjl_scores", "tq_prod_inner_product"):
+                 "tq_project", "tq_copy_rows", "tq_score_packed", "tq_score_packed_noalloc", "tq_qjl_compress", "tq_qjl_scores", "tq_prod_inner_product"):
         getattr(L, name).restype = i32
     _lib = L
     return L
@@ -140,6 +151,17 @@ def require_cuda(t: torch.Tensor, what: str):
     if not t.is_cuda:
         raise RuntimeError(f"{what}: tensor is on {t.device}; the compression kernels run on CUDA (sm_100a) only "
                            "and there is no CPU path")
+
+
+def warn_if_not_cuda(device, what: str):
+    """Constructors call this.  An object built for a CPU device keeps the reference's host-side behaviour
+    (constants, bit widths, memory accounting, window passthrough) but every compute call on it raises: say so
+    when it is built, not at the first call."""
+    if torch.device(device).type != "cuda":
+        import warnings
+        warnings.warn(f"{what}(device={str(device)!r}): the compression kernels run on a CUDA device (sm_100a) only; "
+                      "compress/decompress/score calls on this object will raise (there is no CPU path)",
+                      RuntimeWarning, stacklevel=3)
 
 
 def stream_ptr(device) -> int:

@@ -99,15 +99,41 @@ def quantize_rotated(y: torch.Tensor, codebook: torch.Tensor, bits: int, idx_mod
     return out
 
 
+def _check_score_args(what, q, idx_bytes, norms, pi_t, codebook, bits, outs=()):
+    """Shapes, dtypes, devices and contiguity of everything whose raw pointer goes to the score kernels: a
+    wrong-size or wrong-dtype buffer would otherwise be read or written out of bounds.  Allocates nothing."""
+    N.require_cuda(q, what)
+    if q.dim() != 4 or idx_bytes.dim() != 4:
+        raise ValueError(f"{what}: q must be (B,Hq,Sq,D) and idx_bytes (B,Hkv,Sk,G)")
+    B, Hq, Sq, D = q.shape
+    Bk, Hkv, Sk, G = idx_bytes.shape
+    if Bk != B or Hkv < 1 or Hq % Hkv != 0:
+        raise ValueError(f"{what}: batch {Bk} != {B} or query heads {Hq} not a multiple of KV heads {Hkv}")
+    if idx_bytes.dtype != torch.uint8 or G != N.packed_row_bytes(D, bits):
+        raise ValueError(f"{what}: idx_bytes must be uint8 with {N.packed_row_bytes(D, bits)} bytes per key")
+    if norms.dtype != torch.float16 or tuple(norms.shape) != (B, Hkv, Sk):
+        raise ValueError(f"{what}: norms must be float16 of shape {(B, Hkv, Sk)}")
+    N.dtype_code(q)
+    if pi_t.dtype != torch.float32 or tuple(pi_t.shape) != (D, D) or not pi_t.is_contiguous():
+        raise ValueError(f"{what}: rotation must be a contiguous float32 ({D}, {D}) matrix")
+    if codebook.dtype != torch.float32 or codebook.numel() != N.CODEBOOK_FLOATS or not codebook.is_contiguous():
+        raise ValueError(f"{what}: codebook must be a contiguous float32 block of {N.CODEBOOK_FLOATS} values")
+    for t in (idx_bytes, norms, pi_t, codebook) + tuple(outs):
+        if t.device != q.device:
+            raise ValueError(f"{what}: every tensor must be on {q.device}")
+    for t in outs:
+        if t.dtype != torch.float32 or tuple(t.shape) != (B, Hq, Sq, Sk) or not t.is_contiguous():
+            raise ValueError(f"{what}: outputs must be contiguous float32 of shape {(B, Hq, Sq, Sk)}")
+    return B, Hq, Sq, D, Hkv, Sk
+
+
 def score_packed(q: torch.Tensor, idx_bytes: torch.Tensor, norms: torch.Tensor, pi_t: torch.Tensor,
                  codebook: torch.Tensor, bits: int, scale: float = 1.0, softmax: bool = False):
     """q (B,Hq,Sq,D); packed keys (B,Hkv,Sk,G) + norms (B,Hkv,Sk) -> logits (B,Hq,Sq,Sk) [, probs]."""
-    N.require_cuda(q, "score_packed")
-    B, Hq, Sq, D = q.shape
-    _, Hkv, Sk, _G = idx_bytes.shape
     q = q.contiguous()
     idx_bytes = idx_bytes.contiguous()
     norms = norms.contiguous()
+    B, Hq, Sq, D, Hkv, Sk = _check_score_args("score_packed", q, idx_bytes, norms, pi_t, codebook, bits)
     logits = torch.empty((B, Hq, Sq, Sk), dtype=torch.float32, device=q.device)
     probs = torch.empty_like(logits) if softmax else None
     L = N.lib()
@@ -132,12 +158,11 @@ def score_packed_noalloc(q: torch.Tensor, idx_bytes: torch.Tensor, norms: torch.
     tensor.  Inputs must already be contiguous.  Raises ValueError when the problem
     needs more scratch than the built-in array holds.
     """
-    N.require_cuda(q, "score_packed_noalloc")
-    B, Hq, Sq, D = q.shape
-    _, Hkv, Sk, _G = idx_bytes.shape
-    for t in (q, idx_bytes, norms, logits) + ((probs,) if probs is not None else ()):
+    for t in (q, idx_bytes, norms):
         if not t.is_contiguous():
             raise ValueError("score_packed_noalloc takes contiguous tensors (it will not make copies)")
+    outs = (logits,) + ((probs,) if probs is not None else ())
+    B, Hq, Sq, D, Hkv, Sk = _check_score_args("score_packed_noalloc", q, idx_bytes, norms, pi_t, codebook, bits, outs)
     job = N.ScoreJob(q=q.data_ptr(), q_dtype=N.dtype_code(q), D=D, bits=bits, reserved=0, B=B, Hq=Hq, Sq=Sq, Hkv=Hkv,
                      Sk=Sk, idx_bytes=idx_bytes.data_ptr(), norms=norms.data_ptr(), rotation_t=pi_t.data_ptr(),
                      codebook=codebook.data_ptr(), scale=float(scale), reserved2=0, logits=logits.data_ptr(),

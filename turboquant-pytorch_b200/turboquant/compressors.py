@@ -21,6 +21,7 @@ class TurboQuantCompressorV2:
         self.bits = bits
         self.mse_bits = max(bits - 1, 1)
         self.device = device
+        N.warn_if_not_cuda(device, "TurboQuantCompressorV2")
         self.Pi = generate_rotation_matrix(head_dim, seed=seed, device=device)
         self.centroids = solve_codebook_v2(head_dim, self.mse_bits).to(device)
         self.S = generate_qjl_matrix(head_dim, m=head_dim, seed=seed + 10000, device=device)
@@ -50,6 +51,7 @@ class TurboQuantCompressorMSE:
         self.head_dim = head_dim
         self.bits = bits
         self.device = device
+        N.warn_if_not_cuda(device, "TurboQuantCompressorMSE")
         self.Pi = generate_rotation_matrix(head_dim, seed=seed, device=device)
         self.centroids = solve_codebook_v2(head_dim, bits).to(device)
         self._pi_t = self.Pi.T.contiguous()

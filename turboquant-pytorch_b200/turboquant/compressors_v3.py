@@ -24,6 +24,7 @@ class MSECompressor:
     """L2-normalise, rotate, Lloyd-Max quantise, bit-pack; keeps fp16 norms."""
 
     def __init__(self, head_dim: int, bits: int, seed: int, device: str = "cpu"):
+        N.warn_if_not_cuda(device, "MSECompressor")
         self.head_dim = head_dim
         self.bits = bits
         self.device = device

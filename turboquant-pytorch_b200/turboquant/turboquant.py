@@ -49,6 +49,7 @@ class TurboQuantMSE(nn.Module):
         self.d = d
         self.bits = bits
         self.device = device
+        N.warn_if_not_cuda(device, "TurboQuantMSE")
         self.codebook = LloydMaxCodebook(d, bits)
         pi = generate_rotation_matrix(d, seed=seed, device=device)
         self.register_buffer("Pi", pi)
@@ -93,6 +94,7 @@ class TurboQuantProd(nn.Module):
         self.mse_bits = max(bits - 1, 1)
         self.qjl_dim = qjl_dim or d
         self.device = device
+        N.warn_if_not_cuda(device, "TurboQuantProd")
         self.mse = TurboQuantMSE(d, self.mse_bits, seed=seed, device=device)
         s = generate_qjl_matrix(d, m=self.qjl_dim, seed=seed + 1, device=device)
         self.register_buffer("S", s)
@@ -139,6 +141,7 @@ class TurboQuantKVCache:
         self.d_value = d_value
         self.bits = bits
         self.device = device
+        N.warn_if_not_cuda(device, "TurboQuantKVCache")
         self.key_quantizer = TurboQuantProd(d_key, bits, seed=seed, device=device)
         self.value_quantizer = TurboQuantMSE(d_value, bits, seed=seed + 100, device=device)
         self.key_cache = []
