@@ -35,8 +35,20 @@ def _worker(rank, world, port, out):
         codec = tq.TurboQuantV3(128, key_bits=4, value_bits=2, residual_window=0, layer_idx=layer, n_layers=layers,
                                 protected_layers=0)
         packed += codec.memory_bytes(1, 1, seq)["compressed_bytes"]
+    # the Llama-shaped cache the benchmark splits over the ranks: whole (layer, head-range) blocks per rank
+    sys.path.insert(0, ROOT)
+    import bench
+    cfg = bench.CACHES["kv"]
+    blocks = bench.rank_layers(cfg, rank, world)
+    llama_packed = 0
+    for layer, hrange in blocks:
+        codec = tq.TurboQuantV3(128, key_bits=cfg["key_bits"], value_bits=cfg["value_bits"],
+                                residual_window=cfg["window"], layer_idx=layer, n_layers=cfg["layers"],
+                                protected_layers=cfg["protected"])
+        assert (codec.key_bits, codec.value_bits) == bench.layer_bits(cfg, layer)
+        llama_packed += codec.memory_bytes(cfg["batch"], len(hrange), cfg["seq"])["compressed_bytes"]
     gathered = [None] * world
-    dist.all_gather_object(gathered, (units, packed))
+    dist.all_gather_object(gathered, (units, packed, [(l, list(h)) for l, h in blocks], llama_packed))
     t = torch.tensor([1.0 + rank], dtype=torch.float64)        # stand-in for a per-rank elapsed time
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:
@@ -57,8 +69,26 @@ def test_two_ranks_partition_the_cache_and_reduce_timings():
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    all_units = [u for units, _ in gathered for u in units]
+    all_units = [u for units, *_ in gathered for u in units]
     assert sorted(all_units) == [(l, h) for l in range(36) for h in range(2)]
     assert len(set(all_units)) == 72
-    assert sum(packed for _, packed in gathered) == 58982400         # the whole configs[1] cache
+    assert sum(g[1] for g in gathered) == 58982400                   # the whole configs[1] cache
+    llama_units = [(l, h) for g in gathered for l, hs in g[2] for h in hs]
+    assert sorted(llama_units) == [(l, h) for l in range(32) for h in range(8)] and len(set(llama_units)) == 256
+    assert sum(g[3] for g in gathered) == 14305722368                # the whole configs[2] cache, packed + window
     assert tmax == 2.0
+
+
+def test_rank_blocks_cover_the_cache_for_every_world_size():
+    import sys
+    sys.path.insert(0, ROOT)
+    import bench
+    for name in ("kv", "qwen"):
+        cfg = bench.CACHES[name]
+        for world in (1, 2, 3, 4, 8):
+            seen = []
+            for r in range(world):
+                for layer, heads in bench.rank_layers(cfg, r, world):
+                    assert heads.step == 1 and 0 <= heads.start < heads.stop <= cfg["kv_heads"]
+                    seen += [(layer, h) for h in heads]
+            assert sorted(seen) == [(l, h) for l in range(cfg["layers"]) for h in range(cfg["kv_heads"])]
