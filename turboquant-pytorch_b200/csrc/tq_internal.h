@@ -32,6 +32,10 @@ int simt_prod_inner_product(const float* y, int64_t ny, const int64_t* idx, cons
                             float* out, void* workspace, cudaStream_t st);
 
 
+// packed-key logits on the tensor cores, mma.sync (tq_attn_mma.cu); queries already rotated
+bool mma_score_eligible(const TqScoreJob& job);
+int mma_score_packed(const TqScoreJob& job, const float* qrot, float* stats, int nblk, int keys_per_block, cudaStream_t st);
+
 // strided row copy (tq_copy.cu)
 int copy_rows(const TqCopyJob* jobs, int n_jobs, cudaStream_t st);
 

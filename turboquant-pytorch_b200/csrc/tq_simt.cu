@@ -1041,7 +1041,10 @@ int simt_score_packed(const TqScoreJob& job, cudaStream_t st) {
   if (rc != TQ_OK) return rc;
   const int64_t blocks = job.B * job.Hkv * nblk;
   float* st_ptr = job.probs != nullptr ? stats : nullptr;
-  if (job.D == 128 && ((uintptr_t)job.idx_bytes & 15u) == 0) {
+  if (mma_score_eligible(job)) {
+    rc = mma_score_packed(job, qrot, st_ptr, nblk, SCORE_KEYS_PER_BLOCK, st);
+    if (rc != TQ_OK) return rc;
+  } else if (job.D == 128 && ((uintptr_t)job.idx_bytes & 15u) == 0) {
     switch (job.bits) {
       case 1: k_score_packed_d128<1><<<(unsigned)blocks, NT, 0, st>>>(job, qrot, st_ptr, nblk); break;
       case 2: k_score_packed_d128<2><<<(unsigned)blocks, NT, 0, st>>>(job, qrot, st_ptr, nblk); break;
@@ -1055,7 +1058,7 @@ int simt_score_packed(const TqScoreJob& job, cudaStream_t st) {
   } else {
     k_score_packed<<<(unsigned)blocks, NT, 0, st>>>(job, qrot, st_ptr, nblk);
   }
-  rc = check_launch();
+  if (!mma_score_eligible(job)) rc = check_launch();
   if (rc != TQ_OK || job.probs == nullptr) return rc;
   int chunks = (int)((job.Sk + 4095) / 4096);
   dim3 grid((unsigned)rows, (unsigned)chunks);
