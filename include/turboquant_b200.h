@@ -241,6 +241,46 @@ int tq_score_packed(const TqScoreJob* job, void* stream);
 #define TQ_SCORE_NOALLOC_SCRATCH_BYTES (4u << 20)
 int tq_score_packed_noalloc(const TqScoreJob* job, void* stream);
 
+/* ---- decode attention on packed keys AND packed values ---------------------- */
+typedef struct {
+  const void* q;               /* [dev] (B, Hq, Sq, D) contiguous queries (unrotated)             */
+  int32_t q_dtype;
+  int32_t D;                   /* 128                                                              */
+  int32_t key_bits, value_bits;
+  int64_t B, Hq, Sq, Hkv, Sk;  /* Sk packed tokens; Hq % Hkv == 0                                  */
+  const uint8_t* k_idx;        /* [dev] (B, Hkv, Sk, row_k) TQ_IDX_PACKED                          */
+  const uint16_t* k_norms;     /* [dev] (B, Hkv, Sk) fp16 bits                                     */
+  const uint8_t* v_idx;        /* [dev] (B, Hkv, Sk, row_v)                                        */
+  const uint16_t* v_norms;
+  const float* k_rotation_t;   /* [dev] Pi_k^T of the key compressor                               */
+  const float* v_rotation;     /* [dev] Pi_v of the value compressor: v_hat = c_v[idx] @ Pi_v * norm */
+  const float* k_codebook;     /* [dev] codebook blocks                                            */
+  const float* v_codebook;
+  const void* k_window;        /* [dev] kept 16-bit (or fp32) tokens that follow the packed ones,  */
+  const void* v_window;        /*       element (b,h,w,d) at [b*wstride_b + h*wstride_h + w*wstride_s + d]; NULL: none */
+  int32_t window_dtype;
+  int32_t reserved;
+  int64_t W;
+  int64_t wstride_b, wstride_h, wstride_s;
+  float scale;                 /* logits = scale * q . k                                           */
+  int32_t reserved2;
+  float* out;                  /* [dev] (B, Hq, Sq, D) fp32                                        */
+  void* workspace;             /* [dev] 256-byte aligned scratch                                   */
+  size_t workspace_bytes;      /* >= tq_decode_attention_workspace_bytes(B, Hq, Sq, Sk)            */
+} TqDecodeAttnJob;
+
+size_t tq_decode_attention_workspace_bytes(int64_t B, int64_t Hq, int64_t Sq, int64_t Sk);
+
+/* out = softmax(scale * q K_hat^T) V_hat over the Sk packed tokens followed by the W window tokens, where
+ * K_hat, V_hat are what MSECompressor.decompress would return for the packed rows.  Neither is
+ * materialised: logits come from the packed keys (as tq_score_packed), the probability-weighted sum of
+ * the packed values is accumulated in the rotated domain and Pi_v is applied once per query row.
+ * head_dim 128 only (TQ_EDIM otherwise).
+ * Replaces: the decompress-everything-then-attend step of the generation harness,
+ * turboquant/generation_test_v2.py:131-147, i.e. the composition of turboquant/validate_v3.py:83-87
+ * (scores) with the value path of turboquant/compressors_v3.py:83-105.          */
+int tq_decode_attention(const TqDecodeAttnJob* job, void* stream);
+
 /* ---- K4: MSE stage + QJL sign stage ------------------------------------ */
 typedef struct {
   const void* x; int32_t x_dtype; int32_t D;

@@ -413,6 +413,22 @@ def v3_scores(queries: torch.Tensor, keys_recon: torch.Tensor) -> torch.Tensor:
     return torch.matmul(queries.float(), k.transpose(-2, -1))
 
 
+def v3_decode_attention(queries: torch.Tensor, keys_full: torch.Tensor, values_full: torch.Tensor,
+                        scale: float) -> torch.Tensor:
+    """Attention on what TurboQuantV3.decompress_kv returns: softmax(scale * q K^T) V, fp32.
+
+    The composition the generation harness performs after decompressing every chunk
+    (turboquant/generation_test_v2.py:131-147 feeding the model's attention): scores as in
+    turboquant/validate_v3.py:86-87, values from turboquant/compressors_v3.py:83-105.
+    queries (B, Hq, Sq, D); keys_full / values_full (B, Hkv, S, D); grouped-query layout as v3_scores.
+    """
+    logits = v3_scores(queries, keys_full).double() * scale
+    probs = torch.softmax(logits, dim=-1)
+    rep = queries.shape[1] // values_full.shape[1]
+    v = values_full.double().repeat_interleave(rep, dim=1) if rep > 1 else values_full.double()
+    return torch.matmul(probs, v).float()
+
+
 # --------------------------------------------------------------------------- #
 # V2: MSE + QJL
 # --------------------------------------------------------------------------- #

@@ -421,6 +421,32 @@ int tq_score_packed(const TqScoreJob* job, void* stream) {
   return tq::simt_score_packed(*job, (cudaStream_t)stream);
 }
 
+size_t tq_decode_attention_workspace_bytes(int64_t B, int64_t Hq, int64_t Sq, int64_t Sk) {
+  if (B < 0 || Hq < 0 || Sq < 0 || Sk < 0) return 0;
+  return tq::decode_attention_workspace(B, Hq, Sq, Sk, 2048);
+}
+
+int tq_decode_attention(const TqDecodeAttnJob* job, void* stream) {
+  if (job == nullptr) return TQ_ENULL;
+  if (job->key_bits < 1 || job->key_bits > 8 || job->value_bits < 1 || job->value_bits > 8) return TQ_EBITS;
+  if (job->D != 128) return TQ_EDIM;
+  if (bad_dtype(job->q_dtype)) return TQ_EDTYPE;
+  if (job->B < 0 || job->Hq < 0 || job->Sq < 0 || job->Hkv < 1 || job->Sk < 0 || job->W < 0 || job->Hq % job->Hkv != 0)
+    return TQ_EINVAL;
+  if (job->B * job->Hq * job->Sq == 0) return TQ_OK;
+  const bool has_window = job->k_window != nullptr && job->W > 0;
+  if (job->Sk == 0 && !has_window) return TQ_EINVAL;          // nothing to attend to
+  if (job->q == nullptr || job->out == nullptr || job->v_rotation == nullptr || job->workspace == nullptr) return TQ_ENULL;
+  if (job->Sk > 0 && (job->k_idx == nullptr || job->k_norms == nullptr || job->v_idx == nullptr || job->v_norms == nullptr ||
+                      job->k_rotation_t == nullptr || job->k_codebook == nullptr || job->v_codebook == nullptr))
+    return TQ_ENULL;
+  if (has_window && (job->v_window == nullptr || bad_dtype(job->window_dtype))) return job->v_window == nullptr ? TQ_ENULL : TQ_EDTYPE;
+  if (((uintptr_t)job->workspace & 255u) != 0 || ((uintptr_t)job->k_idx & 15u) != 0 || ((uintptr_t)job->v_idx & 15u) != 0)
+    return TQ_EALIGN;
+  if (job->workspace_bytes < tq::decode_attention_workspace(job->B, job->Hq, job->Sq, job->Sk, 2048)) return TQ_EWORKSPACE;
+  return tq::decode_attention(*job, (cudaStream_t)stream);
+}
+
 int tq_qjl_compress(const TqQjlCompressJob* job, void* stream) {
   if (job == nullptr) return TQ_ENULL;
   int rc = check_common(job->D, job->bits);

@@ -36,6 +36,10 @@ int simt_prod_inner_product(const float* y, int64_t ny, const int64_t* idx, cons
 bool mma_score_eligible(const TqScoreJob& job);
 int mma_score_packed(const TqScoreJob& job, const float* qrot, float* stats, int nblk, int keys_per_block, cudaStream_t st);
 
+// decode attention on packed keys and packed values (tq_attn_mma.cu)
+size_t decode_attention_workspace(int64_t B, int64_t Hq, int64_t Sq, int64_t Sk, int keys_per_block);
+int decode_attention(const TqDecodeAttnJob& job, cudaStream_t st);
+
 // strided row copy (tq_copy.cu)
 int copy_rows(const TqCopyJob* jobs, int n_jobs, cudaStream_t st);
 

@@ -60,6 +60,17 @@ class ScoreJob(C.Structure):
                 ("probs", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
 
 
+class DecodeAttnJob(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("q_dtype", C.c_int32), ("D", C.c_int32), ("key_bits", C.c_int32),
+                ("value_bits", C.c_int32), ("B", C.c_int64), ("Hq", C.c_int64), ("Sq", C.c_int64), ("Hkv", C.c_int64),
+                ("Sk", C.c_int64), ("k_idx", C.c_void_p), ("k_norms", C.c_void_p), ("v_idx", C.c_void_p),
+                ("v_norms", C.c_void_p), ("k_rotation_t", C.c_void_p), ("v_rotation", C.c_void_p),
+                ("k_codebook", C.c_void_p), ("v_codebook", C.c_void_p), ("k_window", C.c_void_p),
+                ("v_window", C.c_void_p), ("window_dtype", C.c_int32), ("reserved", C.c_int32), ("W", C.c_int64),
+                ("wstride_b", C.c_int64), ("wstride_h", C.c_int64), ("wstride_s", C.c_int64), ("scale", C.c_float),
+                ("reserved2", C.c_int32), ("out", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
 class QjlCompressJob(C.Structure):
     _fields_ = [("x", C.c_void_p), ("x_dtype", C.c_int32), ("D", C.c_int32), ("bits", C.c_int32),
                 ("normalize", C.c_int32), ("B", C.c_int64), ("H", C.c_int64), ("S", C.c_int64),
@@ -112,6 +123,10 @@ def lib():
     L.tq_score_workspace_bytes.argtypes = [i64, i64, i64, i64, i32]
     L.tq_score_packed.argtypes = [C.POINTER(ScoreJob), vp]
     L.tq_score_packed_noalloc.argtypes = [C.POINTER(ScoreJob), vp]
+    L.tq_decode_attention_workspace_bytes.restype = sz
+    L.tq_decode_attention_workspace_bytes.argtypes = [i64, i64, i64, i64]
+    L.tq_decode_attention.argtypes = [C.POINTER(DecodeAttnJob), vp]
+    L.tq_decode_attention.restype = i32
     L.tq_qjl_compress.argtypes = [C.POINTER(QjlCompressJob), vp]
     L.tq_qjl_compress_workspace_bytes.restype = sz
     L.tq_qjl_compress_workspace_bytes.argtypes = [i64, i32]

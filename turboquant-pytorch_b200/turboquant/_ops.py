@@ -172,6 +172,68 @@ def score_packed_noalloc(q: torch.Tensor, idx_bytes: torch.Tensor, norms: torch.
     return logits if probs is None else (logits, probs)
 
 
+def decode_attention(q: torch.Tensor, k_comp: Optional[dict], v_comp: Optional[dict], key_codec, val_codec,
+                     k_window: Optional[torch.Tensor], v_window: Optional[torch.Tensor], scale: float) -> torch.Tensor:
+    """softmax(scale * q K_hat^T) V_hat over the packed tokens of (k_comp, v_comp) followed by the kept window tokens.
+
+    q (B, Hq, Sq, 128); k_comp / v_comp are MSECompressor dicts ((B, Hkv, Sk, G) packed rows + norms) or None;
+    the windows are (B, Hkv, W, 128) tensors (views are fine, unit last stride) or None.  Returns fp32 (B, Hq, Sq, 128).
+    """
+    N.require_cuda(q, "decode_attention")
+    B, Hq, Sq, D = q.shape
+    if D != 128:
+        raise ValueError("decode_attention: head_dim must be 128")
+    q = q.contiguous()
+    dev = q.device
+    Sk = 0
+    k_idx = k_norms = v_idx = v_norms = None
+    Hkv = None
+    if k_comp is not None:
+        k_idx, k_norms = k_comp["idx_bytes"].contiguous(), k_comp["vec_norms"].contiguous()
+        v_idx, v_norms = v_comp["idx_bytes"].contiguous(), v_comp["vec_norms"].contiguous()
+        _, Hkv, Sk, Gk = k_idx.shape
+        if tuple(v_idx.shape[:3]) != (B, Hkv, Sk) or k_idx.shape[0] != B:
+            raise ValueError("decode_attention: packed keys and values must cover the same (B, Hkv, Sk) tokens")
+        if Gk != N.packed_row_bytes(D, key_codec.bits) or v_idx.shape[3] != N.packed_row_bytes(D, val_codec.bits):
+            raise ValueError("decode_attention: packed row sizes do not match the code widths")
+        if k_idx.dtype != torch.uint8 or v_idx.dtype != torch.uint8 or k_norms.dtype != torch.float16 or v_norms.dtype != torch.float16:
+            raise ValueError("decode_attention: packed rows must be uint8 and norms float16")
+    W = 0
+    if k_window is not None and k_window.shape[2] > 0:
+        if k_window.shape != v_window.shape or k_window.dtype != v_window.dtype or k_window.stride() != v_window.stride():
+            raise ValueError("decode_attention: key and value windows must have the same shape, dtype and strides")
+        if k_window.stride(3) != 1:
+            k_window, v_window = k_window.contiguous(), v_window.contiguous()
+        W = k_window.shape[2]
+        Hkv = k_window.shape[1] if Hkv is None else Hkv
+        if k_window.shape[0] != B or k_window.shape[1] != Hkv or k_window.shape[3] != D:
+            raise ValueError("decode_attention: window shape does not match the queries / packed tokens")
+    else:
+        k_window = v_window = None
+    if Hkv is None:
+        raise ValueError("decode_attention: nothing to attend to")
+    if Hq % Hkv:
+        raise ValueError(f"decode_attention: {Hq} query heads over {Hkv} KV heads")
+    for tt in (k_idx, k_norms, v_idx, v_norms, k_window, v_window):
+        if tt is not None and tt.device != dev:
+            raise ValueError(f"decode_attention: every tensor must be on {dev}")
+    out = torch.empty((B, Hq, Sq, D), dtype=torch.float32, device=dev)
+    L = N.lib()
+    ws_bytes = L.tq_decode_attention_workspace_bytes(B, Hq, Sq, Sk)
+    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+    job = N.DecodeAttnJob(q=q.data_ptr(), q_dtype=N.dtype_code(q), D=D, key_bits=key_codec.bits, value_bits=val_codec.bits,
+                          B=B, Hq=Hq, Sq=Sq, Hkv=Hkv, Sk=Sk, k_idx=_ptr(k_idx), k_norms=_ptr(k_norms), v_idx=_ptr(v_idx),
+                          v_norms=_ptr(v_norms), k_rotation_t=key_codec._pi_t.data_ptr(), v_rotation=val_codec.Pi.data_ptr(),
+                          k_codebook=key_codec._cb.data_ptr(), v_codebook=val_codec._cb.data_ptr(), k_window=_ptr(k_window),
+                          v_window=_ptr(v_window), window_dtype=N.dtype_code(k_window) if W else N.F16, reserved=0, W=W,
+                          wstride_b=k_window.stride(0) if W else 0, wstride_h=k_window.stride(1) if W else 0,
+                          wstride_s=k_window.stride(2) if W else 0, scale=float(scale), reserved2=0, out=out.data_ptr(),
+                          workspace=ws.data_ptr(), workspace_bytes=ws.numel())
+    with torch.cuda.device(dev):
+        N.check(L.tq_decode_attention(C.byref(job), N.stream_ptr(dev)), "tq_decode_attention")
+    return out
+
+
 def qjl_compress(x: torch.Tensor, pi: torch.Tensor, pi_t: torch.Tensor, codebook: torch.Tensor, qjl_t: torch.Tensor,
                  bits: int, normalize: bool, want_k_mse: bool, idx_mode: Optional[int], signs_fp32: bool,
                  rnorm_fp32: bool):

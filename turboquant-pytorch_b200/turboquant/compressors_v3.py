@@ -156,6 +156,23 @@ class TurboQuantV3:
         _ops.run_dequantize(jobs, outs[0].device)
         return outs
 
+    @torch.no_grad()
+    def decode_attention(self, queries: torch.Tensor, compressed_k: dict, compressed_v: dict, scale: float = None):
+        """Attention output straight from what compress_kv returned, without decompress_kv.
+
+        queries (B, Hq, Sq, head_dim) with Hq a multiple of the cache's KV heads; returns fp32 (B, Hq, Sq, head_dim)
+        equal to  softmax(scale * q K^T) V  over the tokens decompress_kv would return (reconstructed packed
+        tokens followed by the kept window tokens).  scale defaults to head_dim ** -0.5.  Not part of the
+        reference API: the reference decompresses every chunk and attends on the result
+        (turboquant/generation_test_v2.py:131-147); this is that composition in one pass over the packed bytes.
+        """
+        if scale is None:
+            scale = self.head_dim ** -0.5
+        self.key_compressor._need_bits()
+        self.val_compressor._need_bits()
+        return _ops.decode_attention(queries, compressed_k["compressed"], compressed_v["compressed"], self.key_compressor,
+                                     self.val_compressor, compressed_k["fp16"], compressed_v["fp16"], scale)
+
     def memory_bytes(self, B: int, H: int, S: int) -> dict:
         window = min(self.residual_window, S)
         packed_tokens = max(S - window, 0)
