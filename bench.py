@@ -391,6 +391,7 @@ def run_side_workload(args, dev):
     scores: configs[3] (decode logits + softmax straight from 4-bit packed keys, 32 query heads on 8 KV heads,
             131072 keys per head, one launch set per layer instance);
     qjl:    configs[4] (V2 MSE+QJL compress, then asymmetric scores for 64 queries per head, head_dim 256);
+    attend: decode attention output straight from packed keys AND packed values (K4/V2), same shape as scores;
     decode: the incremental cache (turboquant.cache.V3Cache) in a generation loop: context 8192, one token per step.
     """
     import turboquant as tq
@@ -424,6 +425,35 @@ def run_side_workload(args, dev):
                    config={"workload": f"configs[3]: {inst} layer instances x 8 KV heads x 131072 4-bit keys, 32 query heads"},
                    roofline={"bound": "hbm", "achieved": by * steps / t / 1e9, "peak": peak, "unit": "GB/s",
                              "frac": by * steps / t / 1e9 / peak, "traffic": None})
+    elif args.workload == "attend":
+        inst = args.layers or 16
+        sk, hkv, hq, kb, vb = 131072, 8, 32, 4, 2
+        codecs, packed, qs = [], [], []
+        for l in range(inst):
+            codec = tq.TurboQuantV3(HEAD_DIM, key_bits=kb, value_bits=vb, residual_window=0, layer_idx=l, n_layers=36,
+                                    protected_layers=0, device=dev)
+            g = torch.Generator(device=dev).manual_seed(45000 + l)
+            keys = torch.randn(1, hkv, sk, HEAD_DIM, generator=g, device=dev, dtype=torch.float32)
+            keys[:, :, :, :4] *= 10.0
+            vals = torch.randn(1, hkv, sk, HEAD_DIM, generator=g, device=dev, dtype=torch.float32)
+            packed.append(codec.compress_kv(keys.half(), vals.half()))
+            qs.append(torch.randn(1, hq, 1, HEAD_DIM, generator=g, device=dev))
+            codecs.append(codec)
+            del keys, vals
+
+        def step():
+            for c, (ck, cv), q in zip(codecs, packed, qs):
+                c.decode_attention(q, ck, cv)
+        t = _time_steps(step, steps, warmup, flush)
+        keys_n = inst * hkv * sk
+        by = keys_n * (packed_row_bytes(kb) + 2 + packed_row_bytes(vb) + 2)
+        out.update(metric="cached tokens/s attended from packed 4-bit keys and 2-bit values (decode attention output)",
+                   unit="tokens/s", value=keys_n * steps / t, ms_per_step=1e3 * t / steps, dtype="f16xf16->f32",
+                   config={"workload": f"{inst} layer instances x 8 KV heads x 131072 packed tokens (K4/V2), 32 query heads, "
+                                       "one query token: TurboQuantV3.decode_attention"},
+                   roofline={"bound": "hbm", "achieved": by * steps / t / 1e9, "peak": peak, "unit": "GB/s",
+                             "frac": by * steps / t / 1e9 / peak, "traffic": None,
+                             "bytes_per_token": packed_row_bytes(kb) + 2 + packed_row_bytes(vb) + 2})
     elif args.workload == "qjl":
         comp = tq.TurboQuantCompressorV2(256, 3, seed=7, device=dev)
         g = torch.Generator(device=dev).manual_seed(50000)
@@ -459,19 +489,27 @@ def run_side_workload(args, dev):
         toks = [torch.randn(1, heads, 1, HEAD_DIM, generator=g, device=dev).half() for _ in range(8)]
         it = [0]
 
-        def step():
+        def step_all():                           # one library call per phase for all layers
+            t = toks[it[0] % len(toks)]
+            it[0] += 1
+            cache.step([t] * nl, [t] * nl, return_views=False)
+
+        def step_per_layer():                     # the form the transformers attention modules call
             t = toks[it[0] % len(toks)]
             it[0] += 1
             for l in range(nl):
                 cache.update(t, t, l)
-        t = _time_steps(step, steps, warmup, flush)
+        t_all = _time_steps(step_all, steps, warmup, flush)
+        t_per = _time_steps(step_per_layer, steps, warmup, flush)
         out.update(metric="decode-step cache updates/s (one new token appended to every layer, oldest window token "
-                          "quantised and reconstructed in place)", unit="layer-updates/s", value=nl * steps / t,
-                   ms_per_step=1e3 * t / steps, dtype="f16xf16->f32",
+                          "quantised and reconstructed in place)", unit="layer-updates/s", value=nl * steps / t_all,
+                   ms_per_step=1e3 * t_all / steps, dtype="f16xf16->f32",
                    config={"workload": f"incremental cache, {nl} layers x {heads} KV heads, context {ctx}, K4/V2, "
-                                       "residual_window=128; host-side call overhead included"},
+                                       "residual_window=128; V3Cache.step(): three library calls per token for all layers; "
+                                       "host-side call overhead included"},
+                   per_layer_update_ms_per_step=1e3 * t_per / steps,
                    roofline={"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None,
-                             "traffic": None, "note": "latency path: two small launches per layer"})
+                             "traffic": None, "note": "latency path: three small launches per token"})
     print(json.dumps(out))
 
 
@@ -485,7 +523,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="profiling only: skip the host round trip")
     ap.add_argument("--no-parity", action="store_true", help="profiling only: skip the oracle check of the timed buffers")
-    ap.add_argument("--workload", default="kv", choices=["kv", "qwen", "scores", "qjl", "decode"],
+    ap.add_argument("--workload", default="kv", choices=["kv", "qwen", "scores", "attend", "qjl", "decode"],
                     help="kv = the headline workload (configs[2]); qwen = configs[1]; the others measure further "
                          "rows of the path on 1 GPU")
     ap.add_argument("--layers", type=int, default=0, help="layer instances of the scores / decode workloads")

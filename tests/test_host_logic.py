@@ -229,3 +229,52 @@ def test_search_shortcut_parameters_bracket_the_exact_index():
             # up to 31 thresholds kernels look the threshold up across the lanes of a warp; the 63 thresholds of
             # 6-bit codes still have a bracketing cubic and are looked up in shared memory
             assert e.min() >= 0 and e.max() <= (31 if bits <= 5 else 63)
+
+
+def test_codebook_disk_cache_round_trip(tmp_path, monkeypatch):
+    """Solved codebooks come back from the disk cache bit for bit, a damaged file is recomputed, and an empty
+    TURBOQUANT_B200_CACHE_DIR switches the cache off."""
+    z = load_golden("codebooks.npz")
+    monkeypatch.setenv("TURBOQUANT_B200_CACHE_DIR", str(tmp_path))
+    lloyd_max._solve.cache_clear()
+    lloyd_max._solve_inlined_v2.cache_clear()
+    c1, b1 = tq.solve_lloyd_max(64, 4)
+    v1 = lloyd_max.solve_codebook_v2(128, 2)
+    files = sorted(p.name for p in tmp_path.iterdir())
+    assert len(files) == 2 and all(f.endswith(".npy") for f in files)
+    lloyd_max._solve.cache_clear()
+    lloyd_max._solve_inlined_v2.cache_clear()
+    calls = []
+    monkeypatch.setattr(lloyd_max, "_solve_points", lambda *a: calls.append(a) or (0.0,) * 16)
+    c2, b2 = tq.solve_lloyd_max(64, 4)                 # served from disk: the solver is not called
+    assert not calls and torch.equal(c1, c2) and torch.equal(b1, b2)
+    assert np.array_equal(c2.numpy(), z["c_64_4"]) and np.array_equal(lloyd_max.solve_codebook_v2(128, 2).numpy(), v1.numpy())
+    monkeypatch.undo()
+    monkeypatch.setenv("TURBOQUANT_B200_CACHE_DIR", str(tmp_path))
+    for p in tmp_path.iterdir():                       # damage every file: wrong length
+        np.save(open(p, "wb"), np.zeros(3))
+    lloyd_max._solve.cache_clear()
+    c3, _ = tq.solve_lloyd_max(64, 4)
+    assert np.array_equal(c3.numpy(), z["c_64_4"])
+    monkeypatch.setenv("TURBOQUANT_B200_CACHE_DIR", "")
+    lloyd_max._solve.cache_clear()
+    assert lloyd_max._cache_dir() is None
+    c4, _ = tq.solve_lloyd_max(64, 4)
+    assert np.array_equal(c4.numpy(), z["c_64_4"])
+    lloyd_max._solve.cache_clear()
+    lloyd_max._solve_inlined_v2.cache_clear()
+
+
+def test_v1_state_dict_reloads_into_a_fresh_module():
+    """Buffers saved from one module and loaded into one built with another seed make it identical."""
+    a = tq.TurboQuantProd(128, 3, seed=42)
+    b = tq.TurboQuantProd(128, 3, seed=7)
+    assert not torch.equal(a.S, b.S) and not torch.equal(a.mse.Pi, b.mse.Pi)
+    b.load_state_dict(a.state_dict())
+    for k, v in a.state_dict().items():
+        assert torch.equal(v, b.state_dict()[k]), k
+    assert torch.equal(a._s_t, b._s_t) and torch.equal(a.mse._pi_t, b.mse._pi_t) and torch.equal(a.mse._cb, b.mse._cb)
+    m1, m2 = tq.TurboQuantMSE(64, 2, seed=1), tq.TurboQuantMSE(64, 2, seed=2)
+    m2.load_state_dict(m1.state_dict())
+    assert torch.equal(m1.Pi, m2.Pi) and torch.equal(m1.centroids, m2.centroids) and torch.equal(m1.boundaries, m2.boundaries)
+    assert torch.equal(m1._pi_t, m2._pi_t)            # the kernel-side constants follow the loaded buffers

@@ -340,7 +340,7 @@ __global__ void __launch_bounds__(kThreadsQ, 1) k_umma_qjl_scores(const __grid_c
       const int q0 = (unit % batch.n_qblocks) * kQ;
       const int64_t key = (int64_t)kt * kKeys + row;
       const int b = i % kNT;
-      ok = mbar_wait(bar_tfull + 8 * b, (uint32_t)((i / kNT) & 1), abort_flag);
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * b, (uint32_t)((i / kNT) & 1), abort_flag));   // warp-collective TMEM loads follow
       if (!ok) break;
       tc_fence_after();
       const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * kQ);

@@ -281,7 +281,11 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
     for (int i = slot; i < n_local && ok; i += 2) {
       const int64_t row = (int64_t)(t0 + i) * kRowsT + rloc;
       const bool valid = row < p.n;
-      ok = mbar_wait(bar_tfull + 8 * slot, (uint32_t)((i >> 1) & 1), abort_flag);
+      // The exit decision is made uniform before anything collective: per warp (the TMEM loads are
+      // warp-collective) and, where the two warpgroups of a tile later meet at a named barrier (stage 2,
+      // head_dim 256), over those 256 threads, so that nobody waits at that barrier for a warp that left.
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * slot, (uint32_t)((i >> 1) & 1), abort_flag));
+      if constexpr (STAGE == 2 && NBLK == 2) ok = bar_red_and(3 + slot, 256, ok);
       if (!ok) break;
       tc_fence_after();
       const uint32_t tile_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(slot * NBLK * 128);

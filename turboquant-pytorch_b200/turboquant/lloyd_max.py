@@ -5,14 +5,22 @@ Host-side, float64, scipy QUADPACK -- the same numerical recipe as the reference
 centroids it returns are constants of the compressed format: indices are only
 comparable between implementations that share them bit for bit.  Solved
 codebooks are memoised per (d, bits, use_exact, max_iter, tol), since a KV cache
-builds the same few codebooks once per layer.
+builds the same few codebooks once per layer, and kept on disk between processes
+(an 8-bit codebook costs ~0.8 s of quadrature): float64 iterates in
+$TURBOQUANT_B200_CACHE_DIR (default ~/.cache/turboquant_b200), one small file per
+(solver variant, d, bits, use_exact, max_iter, tol, scipy version); set the variable to an
+empty string to switch the disk cache off.  A stored codebook is used only if it has the
+expected length; anything else is recomputed and rewritten.
 """
 
 from __future__ import annotations
 
 import functools
 import math
+import os
 
+import numpy as np
+import scipy
 import torch
 from scipy import integrate, special  # noqa: F401  (special kept for API parity of the module namespace)
 
@@ -47,8 +55,47 @@ def _conditional_means(pdf, cells, previous):
     return means
 
 
+def _cache_dir():
+    d = os.environ.get("TURBOQUANT_B200_CACHE_DIR")
+    if d is None:
+        d = os.path.join(os.path.expanduser("~"), ".cache", "turboquant_b200")
+    return d or None
+
+
+def _disk_cached(name: str, n_values: int, compute):
+    """float64 vector `name` from the disk cache, or compute() stored there (best effort, atomic rename)."""
+    folder = _cache_dir()
+    path = os.path.join(folder, f"{name}_scipy{scipy.__version__}.npy") if folder else None
+    if path is not None:
+        try:
+            got = np.load(path)
+            if got.dtype == np.float64 and got.shape == (n_values,) and np.all(np.isfinite(got)):
+                return tuple(float(v) for v in got)
+        except Exception:
+            pass
+    values = compute()
+    if path is not None:
+        try:
+            os.makedirs(folder, exist_ok=True)
+            tmp = f"{path}.{os.getpid()}.tmp"
+            with open(tmp, "wb") as f:
+                np.save(f, np.asarray(values, dtype=np.float64))
+            os.replace(tmp, path)
+        except Exception:
+            pass
+    return tuple(values)
+
+
 @functools.lru_cache(maxsize=None)
 def _solve(d: int, bits: int, use_exact: bool, max_iter: int, tol: float):
+    levels = 2 ** bits
+    points = _disk_cached(f"lloydmax_d{d}_b{bits}_x{int(use_exact)}_i{max_iter}_t{tol!r}", levels,
+                          lambda: _solve_points(d, bits, use_exact, max_iter, tol))
+    mids = tuple((points[i] + points[i + 1]) / 2.0 for i in range(levels - 1))
+    return points, mids
+
+
+def _solve_points(d: int, bits: int, use_exact: bool, max_iter: int, tol: float):
     levels = 2 ** bits
     pdf = _density(d, use_exact)
     sigma = 1.0 / math.sqrt(d)
@@ -62,8 +109,7 @@ def _solve(d: int, bits: int, use_exact: bool, max_iter: int, tol: float):
         points = updated
         if moved < tol:
             break
-    mids = [(points[i] + points[i + 1]) / 2.0 for i in range(levels - 1)]
-    return tuple(points), tuple(mids)
+    return tuple(points)
 
 
 def solve_lloyd_max(d: int, bits: int, use_exact: bool = False, max_iter: int = 200, tol: float = 1e-10):
@@ -74,6 +120,10 @@ def solve_lloyd_max(d: int, bits: int, use_exact: bool = False, max_iter: int = 
 
 @functools.lru_cache(maxsize=None)
 def _solve_inlined_v2(d: int, bits: int):
+    return _disk_cached(f"lloydmax_v2_d{d}_b{bits}", 2 ** bits, lambda: _solve_inlined_v2_points(d, bits))
+
+
+def _solve_inlined_v2_points(d: int, bits: int):
     """Codebook as the V2 compressors of the reference compute it.
 
     Their private solver (turboquant/compressors.py:57-81) writes the density with

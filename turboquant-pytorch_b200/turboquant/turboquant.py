@@ -58,6 +58,19 @@ class TurboQuantMSE(nn.Module):
         # kernel-side constants; not part of the state dict
         self.register_buffer("_pi_t", pi.T.contiguous(), persistent=False)
         self.register_buffer("_cb", N.codebook_block(self.codebook.centroids, bits).to(device), persistent=False)
+        self.register_load_state_dict_post_hook(TurboQuantMSE._after_load)
+
+    @staticmethod
+    def _after_load(module, _incompatible_keys):
+        module._refresh_kernel_constants()          # a post hook must return None
+
+    def _refresh_kernel_constants(self):
+        """Re-derive the kernel-side constants from Pi and centroids (after load_state_dict changed them)."""
+        with torch.no_grad():
+            self._pi_t.copy_(self.Pi.T)
+            self._cb.copy_(N.codebook_block(self.centroids, self.bits))
+            self.codebook.centroids = self.centroids.detach().cpu().clone()
+            self.codebook.boundaries = self.boundaries.detach().cpu().clone()
 
     def rotate(self, x: torch.Tensor) -> torch.Tensor:
         return _ops.project(x, self._pi_t)
@@ -99,6 +112,12 @@ class TurboQuantProd(nn.Module):
         s = generate_qjl_matrix(d, m=self.qjl_dim, seed=seed + 1, device=device)
         self.register_buffer("S", s)
         self.register_buffer("_s_t", s.T.contiguous(), persistent=False)
+        self.register_load_state_dict_post_hook(TurboQuantProd._after_load)
+
+    @staticmethod
+    def _after_load(module, _incompatible_keys):
+        with torch.no_grad():
+            module._s_t.copy_(module.S.T)
 
     def quantize(self, x: torch.Tensor) -> dict:
         flat = x.reshape(1, 1, -1, self.d)
