@@ -462,7 +462,12 @@ def run_side_workload(args, dev):
         c = comp.compress(x)
         t1 = _time_steps(lambda: comp.compress(x), steps, warmup, flush)
         t2 = _time_steps(lambda: comp.asymmetric_attention_scores(q, c), steps, warmup, flush)
+        cp = comp.compress(x, packed=True)
+        t3 = _time_steps(lambda: comp.compress(x, packed=True), steps, warmup, flush)
+        t4 = _time_steps(lambda: comp.asymmetric_attention_scores(q, cp), steps, warmup, flush)
         n = 16 * 16384
+        per_key_ref = comp.stored_bytes(c) // n
+        per_key_packed = comp.stored_bytes(cp) // n
         tpeak = float(peaks.get("bf16_tflops_sustained", 1400.0))
         out.update(metric="V2 MSE+QJL: vectors/s compress, keys/s scored (64 queries)", unit="vectors/s",
                    value=n * steps / t1, ms_per_step=1e3 * t1 / steps, dtype="f32",
@@ -471,6 +476,13 @@ def run_side_workload(args, dev):
                    scores={"keys/s": n * steps / t2, "GB/s": n * 1026 * steps / t2 / 1e9, "ms": 1e3 * t2 / steps,
                            "frac_of_hbm_peak": n * 1026 * steps / t2 / 1e9 / peak,
                            "note": "tcgen05 kernel (k_umma_qjl_scores) plus its query projection and image kernels"},
+                   packed={"stored_bytes_per_key": per_key_packed, "reference_form_bytes_per_key": per_key_ref,
+                           "fp16_key_bytes": 512, "compress_vectors/s": n * steps / t3, "compress_ms": 1e3 * t3 / steps,
+                           "scores_keys/s": n * steps / t4, "scores_ms": 1e3 * t4 / steps,
+                           "scores_GB/s": n * (per_key_packed + 64 * 4) * steps / t4 / 1e9,
+                           "scores_frac_of_hbm_peak": n * (per_key_packed + 64 * 4) * steps / t4 / 1e9 / peak,
+                           "note": "compress(packed=True): MSE indices bit-packed + sign bits + fp32 norm; scores by "
+                                   "k_qjl_score_packed straight from the packed rows (bytes = packed key + 64 fp32 scores)"},
                    roofline={"bound": "tensor", "achieved": n * 393216 * steps / t1 / 1e12, "peak": tpeak,
                              "unit": "TFLOP/s", "frac": n * 393216 * steps / t1 / 1e12 / tpeak, "traffic": None,
                              "note": "compress = three tcgen05 contraction launches (k_umma_v2_stage); flops are "

@@ -301,18 +301,54 @@ typedef struct {
   void* rnorm_out;        /* [dev] (N)                                                        */
   void* workspace;        /* [dev] scratch for the tensor-core path, or NULL (FP32 kernels)   */
   size_t workspace_bytes; /* >= tq_qjl_compress_workspace_bytes(N, D) to enable that path     */
+  float* vec_norms_out;   /* [dev] optional fp32 ||x|| per vector (N), normalize == 1 only: what the
+                             packed form keeps in place of k_mse                              */
 } TqQjlCompressJob;
 
 /* Scratch the tensor-core path of tq_qjl_compress needs for N vectors (operand images of the three
  * matrices, two fp16 piece arrays of N x D, N norms); 0 when head_dim has no such path.  That path
  * serves contiguous fp16 vectors with head_dim 128 or 256, normalize = 1, M = D, int8 signs, fp16
- * norms and k_mse_out set; every other job, and any job without enough scratch, runs on the FP32
- * kernels with identical semantics.                                                            */
+ * residual norms, idx_out NULL or TQ_IDX_U8; every other job, and any job without enough scratch,
+ * runs on the FP32 kernels with identical semantics.                                           */
 size_t tq_qjl_compress_workspace_bytes(int64_t n_vectors, int D);
 
 /* Replaces: TurboQuantCompressorV2.compress turboquant/compressors.py:83-120;
  * TurboQuantProd.quantize turboquant/turboquant.py:134-159.                    */
 int tq_qjl_compress(const TqQjlCompressJob* job, void* stream);
+
+/* ---- packed storage of the MSE+QJL representation ----------------------- */
+/* idx_u8 [dev] (n, D) one index per byte, signs [dev] (n, D) int8 +-1  ->
+ * idx_packed [dev] (n, ceil(D / (8/bits))) in the TQ_IDX_PACKED layout and sign_bits [dev] (n, D/8), coordinate j
+ * in bit 7 - j % 8 of byte j / 8, set for +1.  D a multiple of 8.  Either output may be NULL.
+ * Replaces nothing the reference runs: it is the storage layout the reference's own size accounting assumes
+ * (turboquant/validate.py:120-134) in place of the fp16 k_mse + int8 signs it stores
+ * (turboquant/compressors.py:115-120) and the int64 indices + fp32 signs of turboquant/turboquant.py:155-159. */
+int tq_pack_mse_qjl(const uint8_t* idx_u8, const int8_t* signs, int64_t n, int D, int bits, uint8_t* idx_packed,
+                    uint8_t* sign_bits, void* stream);
+
+typedef struct {
+  const void* q; int32_t q_dtype; int32_t D;    /* (BH, Sq, D) queries; D = 128 or 256              */
+  int32_t bits;                                  /* width of the MSE stage                            */
+  int32_t reserved;
+  int64_t BH, Sq, Sk;
+  const uint8_t* idx_packed;   /* [dev] (BH, Sk, row) TQ_IDX_PACKED                                   */
+  const uint8_t* sign_bits;    /* [dev] (BH, Sk, D/8)                                                 */
+  const float* vec_norms;      /* [dev] fp32 (BH, Sk)                                                 */
+  const uint16_t* rnorm;       /* [dev] fp16 (BH, Sk)                                                 */
+  const float* rotation_t;     /* [dev] Pi^T (D, D)                                                   */
+  const float* qjl_t;          /* [dev] S^T (D, D)                                                    */
+  const float* codebook;       /* [dev] codebook block of the MSE stage                               */
+  float* scores;               /* [dev] (BH, Sq, Sk)                                                  */
+  void* workspace; size_t workspace_bytes;   /* >= tq_qjl_scores_packed_workspace_bytes               */
+} TqQjlPackedScoreJob;
+
+size_t tq_qjl_scores_packed_workspace_bytes(int64_t BH, int64_t Sq, int D);
+
+/* The estimator of tq_qjl_scores evaluated straight from the packed form:
+ * <q, k_mse> = ||x|| * <q Pi^T, c[idx]> needs no reconstructed key, the sign term reads one bit per
+ * coordinate.  Replaces: TurboQuantCompressorV2.asymmetric_attention_scores
+ * turboquant/compressors.py:122-158 on the layout of turboquant/validate.py:120-134.               */
+int tq_qjl_scores_packed(const TqQjlPackedScoreJob* job, void* stream);
 
 /* ---- K5: asymmetric scores from the MSE+QJL representation ------------- */
 typedef struct {

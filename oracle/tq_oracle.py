@@ -465,6 +465,34 @@ def v2_scores(queries: torch.Tensor, comp: dict, s_mat: torch.Tensor) -> torch.T
     return term1 + scale * ip * r_norm.unsqueeze(-2)
 
 
+def v2_pack(idx: torch.Tensor, signs: torch.Tensor, bits: int):
+    """Packed form of the V2 representation, which the reference does not store but whose size its accounting assumes
+    (turboquant/validate.py:120-134): indices bit-packed as in turboquant/compressors_v3.py:64-74; signs one bit per
+    coordinate, coordinate j in bit 7 - j % 8 of byte j / 8, set for +1.  (n, D) int -> ((n, G) uint8, (n, D/8) uint8)."""
+    rows, _ = pack_indices(idx.cpu().numpy(), bits)
+    sbits = np.packbits((signs.cpu().numpy() > 0).astype(np.uint8), axis=-1, bitorder="big")
+    return torch.from_numpy(rows), torch.from_numpy(sbits)
+
+
+def v2_scores_packed(queries: torch.Tensor, rows: torch.Tensor, sbits: torch.Tensor, vec_norms: torch.Tensor,
+                     r_norm: torch.Tensor, pi: torch.Tensor, centroids: torch.Tensor, s_mat: torch.Tensor,
+                     bits: int) -> torch.Tensor:
+    """asymmetric_attention_scores (turboquant/compressors.py:122-158) evaluated from the packed form, in float64:
+    k_mse = (centroids[idx] @ Pi) * vec_norms is rebuilt without the fp16 rounding of the stored k_mse.
+    queries (B,H,Sq,D); rows (B,H,Sk,G); sbits (B,H,Sk,D/8); vec_norms, r_norm (B,H,Sk)."""
+    b, h, sk, _ = rows.shape
+    d = queries.shape[-1]
+    idx = torch.from_numpy(unpack_indices(rows.reshape(b * h * sk, -1).cpu().numpy(), bits, d))
+    k_mse = (centroids.double()[idx] @ pi.double()) * vec_norms.double().reshape(-1, 1)
+    signs = np.unpackbits(sbits.reshape(b * h * sk, -1).cpu().numpy(), axis=-1, bitorder="big")[:, :d]
+    signs = torch.from_numpy(signs.astype(np.float64)) * 2 - 1
+    q = queries.double().cpu()
+    term1 = torch.matmul(q, k_mse.reshape(b, h, sk, d).transpose(-2, -1))
+    ip = torch.matmul(torch.matmul(q, s_mat.double().T), signs.reshape(b, h, sk, d).transpose(-2, -1))
+    scale = math.sqrt(math.pi / 2) / s_mat.shape[0]
+    return term1 + scale * ip * r_norm.double().cpu().unsqueeze(-2)
+
+
 def v2mse_compress(states: torch.Tensor, pi: torch.Tensor, centroids: torch.Tensor) -> dict:
     """TurboQuantCompressorMSE.compress (unpacked uint8).  turboquant/compressors.py:200-213."""
     b, h, s, d = states.shape

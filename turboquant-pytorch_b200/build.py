@@ -19,7 +19,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "turboquant", "libturboquant_b200.so")
-SOURCES = ["tq_api.cu", "tq_simt.cu", "tq_umma.cu", "tq_qjl_umma.cu", "tq_v2_umma.cu", "tq_score_static.cu", "tq_copy.cu", "tq_attn_mma.cu"]
+SOURCES = ["tq_api.cu", "tq_simt.cu", "tq_umma.cu", "tq_qjl_umma.cu", "tq_v2_umma.cu", "tq_score_static.cu", "tq_copy.cu", "tq_attn_mma.cu", "tq_qjl_packed.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -469,6 +469,39 @@ size_t tq_qjl_compress_workspace_bytes(int64_t n_vectors, int D) {
   return tq::umma_v2_compress_workspace(n_vectors, D);
 }
 
+int tq_pack_mse_qjl(const uint8_t* idx_u8, const int8_t* signs, int64_t n, int D, int bits, uint8_t* idx_packed,
+                    uint8_t* sign_bits, void* stream) {
+  int rc = check_common(D, bits);
+  if (rc != TQ_OK) return rc;
+  if (n < 0 || D % 8 != 0) return TQ_EINVAL;
+  if (n == 0) return TQ_OK;
+  if ((idx_packed != nullptr && idx_u8 == nullptr) || (sign_bits != nullptr && signs == nullptr)) return TQ_ENULL;
+  if (idx_packed == nullptr && sign_bits == nullptr) return TQ_OK;
+  return tq::pack_mse_qjl(idx_u8, signs, n, D, bits, idx_packed, sign_bits, (cudaStream_t)stream);
+}
+
+size_t tq_qjl_scores_packed_workspace_bytes(int64_t BH, int64_t Sq, int D) {
+  if (BH < 0 || Sq < 0 || D < 1) return 0;
+  return tq::qjl_scores_packed_workspace(BH, Sq, D);
+}
+
+int tq_qjl_scores_packed(const TqQjlPackedScoreJob* job, void* stream) {
+  if (job == nullptr) return TQ_ENULL;
+  if (job->bits < 1 || job->bits > 8) return TQ_EBITS;
+  if (job->D != 128 && job->D != 256) return TQ_EDIM;
+  if (bad_dtype(job->q_dtype)) return TQ_EDTYPE;
+  if (job->BH < 0 || job->Sq < 0 || job->Sk < 0) return TQ_EINVAL;
+  if (job->BH == 0 || job->Sq == 0 || job->Sk == 0) return TQ_OK;
+  if (job->q == nullptr || job->idx_packed == nullptr || job->sign_bits == nullptr || job->vec_norms == nullptr ||
+      job->rnorm == nullptr || job->rotation_t == nullptr || job->qjl_t == nullptr || job->codebook == nullptr ||
+      job->scores == nullptr || job->workspace == nullptr)
+    return TQ_ENULL;
+  if (((uintptr_t)job->workspace & 255u) != 0 || ((uintptr_t)job->idx_packed & 15u) != 0 || ((uintptr_t)job->sign_bits & 7u) != 0)
+    return TQ_EALIGN;
+  if (job->workspace_bytes < tq::qjl_scores_packed_workspace(job->BH, job->Sq, job->D)) return TQ_EWORKSPACE;
+  return tq::qjl_scores_packed(*job, (cudaStream_t)stream);
+}
+
 size_t tq_qjl_scores_workspace_bytes(int64_t BH, int64_t Sq, int D) {
   if (BH < 0 || Sq < 0 || D < 1) return 0;
   return tq::simt_qjl_scores_workspace(BH, Sq, D) + tq::umma_qjl_scores_image_bytes(BH, Sq, D);

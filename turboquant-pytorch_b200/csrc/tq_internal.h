@@ -40,6 +40,12 @@ int mma_score_packed(const TqScoreJob& job, const float* qrot, float* stats, int
 size_t decode_attention_workspace(int64_t B, int64_t Hq, int64_t Sq, int64_t Sk, int keys_per_block);
 int decode_attention(const TqDecodeAttnJob& job, cudaStream_t st);
 
+// packed MSE+QJL storage and scores from it (tq_qjl_packed.cu)
+int pack_mse_qjl(const uint8_t* idx_u8, const int8_t* signs, int64_t n, int D, int bits, uint8_t* idx_packed,
+                 uint8_t* sign_bits, cudaStream_t st);
+size_t qjl_scores_packed_workspace(int64_t BH, int64_t Sq, int D);
+int qjl_scores_packed(const TqQjlPackedScoreJob& job, cudaStream_t st);
+
 // strided row copy (tq_copy.cu)
 int copy_rows(const TqCopyJob* jobs, int n_jobs, cudaStream_t st);
 

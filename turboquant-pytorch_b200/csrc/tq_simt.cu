@@ -780,6 +780,7 @@ __global__ void __launch_bounds__(NT) k_qjl_compress(TqQjlCompressJob job) {
         float rn = __fsqrt_rn(ssq);
         if (job.rnorm_dtype == TQ_F16) reinterpret_cast<uint16_t*>(job.rnorm_out)[n] = __half_as_ushort(__float2half_rn(rn));
         else reinterpret_cast<float*>(job.rnorm_out)[n] = rn;
+        if (job.vec_norms_out != nullptr && job.normalize) job.vec_norms_out[n] = nrm[r];
       }
     }
     {

@@ -62,7 +62,8 @@ struct V2Stage {
   uint16_t* p_hi;            // scratch (n, D): centroid pieces after stage 1, residual pieces after stage 2
   uint16_t* p_lo;
   float* norms;              // scratch (n): ||x||
-  uint16_t* k_mse_out;       // stage 2
+  uint8_t* idx_u8_out;       // stage 1: optional, one index per byte (n, D)
+  uint16_t* k_mse_out;       // stage 2: optional
   uint16_t* rnorm_out;       // stage 2, fp16 bits
   int8_t* signs_out;         // stage 3
   int32_t* status;
@@ -308,6 +309,7 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
         for (int c = 0; c < 8; ++c) {
           tmem_ld16(tacc + c * 16, v);
           uint32_t w[16];
+          uint32_t ib[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
             const float y = __uint_as_float(v[e]) * inv;
@@ -334,7 +336,10 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
               idx = lo;
             }
             w[e] = lut_s[idx];
+            ib[e >> 2] |= (uint32_t)idx << (8 * (e & 3));
           }
+          if (valid && p.idx_u8_out != nullptr)
+            *reinterpret_cast<uint4*>(p.idx_u8_out + row * D + col0 + c * 16) = make_uint4(ib[0], ib[1], ib[2], ib[3]);
           if (valid) {
             uint32_t ph[8], pl[8];
 #pragma unroll
@@ -376,10 +381,12 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
               const __half2 ll = __floats2half2_rn(r0 - __low2float(hh), r1 - __high2float(hh));
               rl[j] = *reinterpret_cast<const uint32_t*>(&ll);
             }
-            uint4* dk = reinterpret_cast<uint4*>(p.k_mse_out + row * D + col0 + c * 16);
             uint4* dh = reinterpret_cast<uint4*>(p.p_hi + row * D + col0 + c * 16);
             uint4* dl = reinterpret_cast<uint4*>(p.p_lo + row * D + col0 + c * 16);
-            dk[0] = make_uint4(kq[0], kq[1], kq[2], kq[3]); dk[1] = make_uint4(kq[4], kq[5], kq[6], kq[7]);
+            if (p.k_mse_out != nullptr) {
+              uint4* dk = reinterpret_cast<uint4*>(p.k_mse_out + row * D + col0 + c * 16);
+              dk[0] = make_uint4(kq[0], kq[1], kq[2], kq[3]); dk[1] = make_uint4(kq[4], kq[5], kq[6], kq[7]);
+            }
             dh[0] = make_uint4(rh[0], rh[1], rh[2], rh[3]); dh[1] = make_uint4(rh[4], rh[5], rh[6], rh[7]);
             dl[0] = make_uint4(rl[0], rl[1], rl[2], rl[3]); dl[1] = make_uint4(rl[4], rl[5], rl[6], rl[7]);
           }
@@ -481,7 +488,8 @@ int run(const TqQjlCompressJob& job, cudaStream_t st) {
   p.x = reinterpret_cast<const uint16_t*>(job.x);
   p.p_hi = p_hi;
   p.p_lo = p_lo;
-  p.norms = norms;
+  p.norms = job.vec_norms_out != nullptr ? job.vec_norms_out : norms;
+  p.idx_u8_out = reinterpret_cast<uint8_t*>(job.idx_out);
   p.k_mse_out = job.k_mse_out;
   p.rnorm_out = reinterpret_cast<uint16_t*>(job.rnorm_out);
   p.signs_out = reinterpret_cast<int8_t*>(job.signs_out);
@@ -519,7 +527,7 @@ bool umma_v2_compress_eligible(const TqQjlCompressJob& job) {
   if (force_simt()) return false;
   if (job.D != 128 && job.D != 256) return false;
   if (job.x_dtype != TQ_F16 || job.normalize != 1 || job.signs_dtype != 0 || job.rnorm_dtype != TQ_F16) return false;
-  if (job.M != job.D || job.k_mse_out == nullptr || job.idx_out != nullptr) return false;
+  if (job.M != job.D || (job.idx_out != nullptr && job.idx_mode != TQ_IDX_U8)) return false;
   if (job.bits < 1 || job.bits > 8) return false;
   const int64_t n = job.B * job.H * job.S;
   if (n <= 0) return false;
@@ -527,7 +535,9 @@ bool umma_v2_compress_eligible(const TqQjlCompressJob& job) {
   if (job.S > 1 && job.stride_s != job.D) return false;
   if (job.H > 1 && job.stride_h != job.S * job.D) return false;
   if (job.B > 1 && job.stride_b != job.H * job.S * job.D) return false;
-  if (((uintptr_t)job.x & 15u) || ((uintptr_t)job.k_mse_out & 15u) || ((uintptr_t)job.signs_out & 15u)) return false;
+  if (((uintptr_t)job.x & 15u) || ((uintptr_t)job.k_mse_out & 15u) || ((uintptr_t)job.signs_out & 15u) ||
+      ((uintptr_t)job.idx_out & 15u))
+    return false;
   if (job.workspace == nullptr || job.workspace_bytes < umma_v2_compress_workspace(n, job.D)) return false;
   return true;
 }

@@ -78,7 +78,15 @@ class QjlCompressJob(C.Structure):
                 ("rotation_t", C.c_void_p), ("rotation", C.c_void_p), ("codebook", C.c_void_p), ("qjl_t", C.c_void_p),
                 ("M", C.c_int32), ("signs_dtype", C.c_int32), ("rnorm_dtype", C.c_int32), ("idx_mode", C.c_int32),
                 ("k_mse_out", C.c_void_p), ("idx_out", C.c_void_p), ("signs_out", C.c_void_p), ("rnorm_out", C.c_void_p),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("vec_norms_out", C.c_void_p)]
+
+
+class QjlPackedScoreJob(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("q_dtype", C.c_int32), ("D", C.c_int32), ("bits", C.c_int32), ("reserved", C.c_int32),
+                ("BH", C.c_int64), ("Sq", C.c_int64), ("Sk", C.c_int64), ("idx_packed", C.c_void_p),
+                ("sign_bits", C.c_void_p), ("vec_norms", C.c_void_p), ("rnorm", C.c_void_p), ("rotation_t", C.c_void_p),
+                ("qjl_t", C.c_void_p), ("codebook", C.c_void_p), ("scores", C.c_void_p), ("workspace", C.c_void_p),
+                ("workspace_bytes", C.c_size_t)]
 
 
 class QjlScoreJob(C.Structure):
@@ -133,6 +141,12 @@ def lib():
     L.tq_qjl_scores_workspace_bytes.restype = sz
     L.tq_qjl_scores_workspace_bytes.argtypes = [i64, i64, i32]
     L.tq_qjl_scores.argtypes = [C.POINTER(QjlScoreJob), vp]
+    L.tq_pack_mse_qjl.argtypes = [vp, vp, i64, i32, i32, vp, vp, vp]
+    L.tq_pack_mse_qjl.restype = i32
+    L.tq_qjl_scores_packed_workspace_bytes.restype = sz
+    L.tq_qjl_scores_packed_workspace_bytes.argtypes = [i64, i64, i32]
+    L.tq_qjl_scores_packed.argtypes = [C.POINTER(QjlPackedScoreJob), vp]
+    L.tq_qjl_scores_packed.restype = i32
     L.tq_prod_inner_product.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, vp, vp, vp, vp, vp, sz, vp]
     for name in ("tq_packed_row_bytes", "tq_build_codebook", "tq_quantize_rotated", "tq_quantize", "tq_dequantize",
                  "tq_project", "tq_copy_rows", "tq_score_packed", "tq_score_packed_noalloc", "tq_qjl_compress", "tq_qjl_scores", "tq_prod_inner_product"):

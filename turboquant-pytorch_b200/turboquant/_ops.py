@@ -236,8 +236,9 @@ def decode_attention(q: torch.Tensor, k_comp: Optional[dict], v_comp: Optional[d
 
 def qjl_compress(x: torch.Tensor, pi: torch.Tensor, pi_t: torch.Tensor, codebook: torch.Tensor, qjl_t: torch.Tensor,
                  bits: int, normalize: bool, want_k_mse: bool, idx_mode: Optional[int], signs_fp32: bool,
-                 rnorm_fp32: bool):
-    """MSE stage + QJL signs for a (B,H,S,D) tensor.  Returns (k_mse|None, idx|None, signs (n,M), rnorm (n,))."""
+                 rnorm_fp32: bool, want_vec_norms: bool = False):
+    """MSE stage + QJL signs for a (B,H,S,D) tensor.  Returns (k_mse|None, idx|None, signs (n,M), rnorm (n,)), and
+    the fp32 vector norms (n,) as a fifth value with want_vec_norms."""
     N.require_cuda(x, "qjl_compress")
     B, H, S, D = x.shape
     x, sb, sh, ss = N.bhs_strides(x)
@@ -253,7 +254,8 @@ def qjl_compress(x: torch.Tensor, pi: torch.Tensor, pi_t: torch.Tensor, codebook
     # scratch for the tensor-core path (fp16 vectors, head_dim 128 / 256, the V2 output formats); without it
     # the library runs the FP32 kernels
     ws, ws_bytes = None, 0
-    if x.dtype == torch.float16 and normalize and want_k_mse and idx_mode is None and not signs_fp32 and not rnorm_fp32:
+    vnorm = torch.empty((n,), dtype=torch.float32, device=dev) if want_vec_norms else None
+    if x.dtype == torch.float16 and normalize and idx_mode in (None, N.IDX_U8) and not signs_fp32 and not rnorm_fp32:
         ws_bytes = N.lib().tq_qjl_compress_workspace_bytes(n, D)
         if ws_bytes:
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
@@ -263,10 +265,60 @@ def qjl_compress(x: torch.Tensor, pi: torch.Tensor, pi_t: torch.Tensor, codebook
                            signs_dtype=int(signs_fp32), rnorm_dtype=N.F32 if rnorm_fp32 else N.F16,
                            idx_mode=idx_mode if idx_mode is not None else N.IDX_U8, k_mse_out=_ptr(k_mse),
                            idx_out=_ptr(idx), signs_out=signs.data_ptr(), rnorm_out=rnorm.data_ptr(),
-                           workspace=_ptr(ws), workspace_bytes=ws_bytes)
+                           workspace=_ptr(ws), workspace_bytes=ws_bytes, vec_norms_out=_ptr(vnorm))
     with torch.cuda.device(dev):
         N.check(N.lib().tq_qjl_compress(C.byref(job), N.stream_ptr(dev)), "tq_qjl_compress")
+    if want_vec_norms:
+        return k_mse, idx, signs, rnorm, vnorm
     return k_mse, idx, signs, rnorm
+
+
+def pack_mse_qjl(idx_u8: Optional[torch.Tensor], signs_i8: Optional[torch.Tensor], D: int, bits: int):
+    """(n, D) uint8 indices and (n, D) int8 signs -> (packed index rows (n, G) | None, sign bits (n, D/8) | None)."""
+    src = idx_u8 if idx_u8 is not None else signs_i8
+    N.require_cuda(src, "pack_mse_qjl")
+    n = src.shape[0]
+    dev = src.device
+    packed = torch.empty((n, N.packed_row_bytes(D, bits)), dtype=torch.uint8, device=dev) if idx_u8 is not None else None
+    sbits = torch.empty((n, D // 8), dtype=torch.uint8, device=dev) if signs_i8 is not None else None
+    if idx_u8 is not None:
+        idx_u8 = idx_u8.contiguous()
+    if signs_i8 is not None:
+        signs_i8 = signs_i8.contiguous()
+    with torch.cuda.device(dev):
+        N.check(N.lib().tq_pack_mse_qjl(_ptr(idx_u8), _ptr(signs_i8), n, D, bits, _ptr(packed), _ptr(sbits),
+                                        N.stream_ptr(dev)), "tq_pack_mse_qjl")
+    return packed, sbits
+
+
+def qjl_scores_packed(q: torch.Tensor, idx_packed: torch.Tensor, sign_bits: torch.Tensor, vec_norms: torch.Tensor,
+                      rnorm: torch.Tensor, pi_t: torch.Tensor, qjl_t: torch.Tensor, codebook: torch.Tensor, bits: int):
+    """q (B,H,Sq,D) against the packed MSE+QJL form ((B,H,Sk,G) index rows, (B,H,Sk,D/8) sign bits, fp32 vector norms,
+    fp16 residual norms) -> (B,H,Sq,Sk) fp32."""
+    N.require_cuda(q, "qjl_scores_packed")
+    B, H, Sq, D = q.shape
+    Sk = idx_packed.shape[2]
+    if D not in (128, 256):
+        raise ValueError("qjl_scores_packed: head_dim must be 128 or 256")
+    if tuple(idx_packed.shape) != (B, H, Sk, N.packed_row_bytes(D, bits)) or tuple(sign_bits.shape) != (B, H, Sk, D // 8):
+        raise ValueError("qjl_scores_packed: packed shapes do not match the queries")
+    if idx_packed.dtype != torch.uint8 or sign_bits.dtype != torch.uint8 or vec_norms.dtype != torch.float32 or \
+            rnorm.dtype != torch.float16 or tuple(vec_norms.shape) != (B, H, Sk) or tuple(rnorm.shape) != (B, H, Sk):
+        raise ValueError("qjl_scores_packed: uint8 rows, fp32 vector norms and fp16 residual norms of shape (B, H, Sk)")
+    q = q.contiguous()
+    idx_packed, sign_bits, vec_norms, rnorm = (t.contiguous() for t in (idx_packed, sign_bits, vec_norms, rnorm))
+    out = torch.empty((B, H, Sq, Sk), dtype=torch.float32, device=q.device)
+    L = N.lib()
+    ws_bytes = L.tq_qjl_scores_packed_workspace_bytes(B * H, Sq, D)
+    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=q.device)
+    job = N.QjlPackedScoreJob(q=q.data_ptr(), q_dtype=N.dtype_code(q), D=D, bits=bits, reserved=0, BH=B * H, Sq=Sq, Sk=Sk,
+                              idx_packed=idx_packed.data_ptr(), sign_bits=sign_bits.data_ptr(),
+                              vec_norms=vec_norms.data_ptr(), rnorm=rnorm.data_ptr(), rotation_t=pi_t.data_ptr(),
+                              qjl_t=qjl_t.data_ptr(), codebook=codebook.data_ptr(), scores=out.data_ptr(),
+                              workspace=ws.data_ptr(), workspace_bytes=ws.numel())
+    with torch.cuda.device(q.device):
+        N.check(L.tq_qjl_scores_packed(C.byref(job), N.stream_ptr(q.device)), "tq_qjl_scores_packed")
+    return out
 
 
 def qjl_scores(q: torch.Tensor, k_mse: torch.Tensor, signs: torch.Tensor, rnorm: torch.Tensor,

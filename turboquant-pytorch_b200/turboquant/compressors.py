@@ -30,16 +30,62 @@ class TurboQuantCompressorV2:
         self._cb = N.codebook_block(self.centroids, self.mse_bits).to(device)
 
     @torch.no_grad()
-    def compress(self, states: torch.Tensor) -> dict:
+    def compress(self, states: torch.Tensor, packed: bool = False) -> dict:
+        """The reference's dict ("k_mse" fp16, "qjl_signs" int8, "residual_norm" fp16, "shape"), or with packed=True
+        the packed form of the same information (not in the reference, whose stored form is larger than the 16-bit
+        keys; its own size accounting, turboquant/validate.py:120-134, assumes this layout):
+          "mse_idx_bytes" (B,H,S,G) uint8   MSE indices, bit-packed as in compressors_v3.py:64-74
+          "sign_bits"     (B,H,S,D/8) uint8 QJL signs, coordinate j in bit 7 - j % 8 of byte j / 8, set for +1
+          "vec_norms"     (B,H,S) fp32      ||x||: k_mse = (centroids[idx] @ Pi) * vec_norms
+          "residual_norm" (B,H,S) fp16, "shape", "packed": True
+        asymmetric_attention_scores takes either form; unpack() turns the packed one into the reference's."""
         B, H, S, D = states.shape
-        k_mse, _idx, signs, rnorm = _ops.qjl_compress(states, self.Pi, self.PiT, self._cb, self._s_t, self.mse_bits,
-                                                      normalize=True, want_k_mse=True, idx_mode=None,
-                                                      signs_fp32=False, rnorm_fp32=False)
+        if not packed:
+            k_mse, _idx, signs, rnorm = _ops.qjl_compress(states, self.Pi, self.PiT, self._cb, self._s_t, self.mse_bits,
+                                                          normalize=True, want_k_mse=True, idx_mode=None,
+                                                          signs_fp32=False, rnorm_fp32=False)
+            return {"k_mse": k_mse.reshape(B, H, S, D), "qjl_signs": signs.reshape(B, H, S, D),
+                    "residual_norm": rnorm.reshape(B, H, S), "shape": (B, H, S, D)}
+        if D % 8:
+            raise ValueError("packed=True needs head_dim to be a multiple of 8")
+        _k, idx, signs, rnorm, vnorm = _ops.qjl_compress(states, self.Pi, self.PiT, self._cb, self._s_t, self.mse_bits,
+                                                         normalize=True, want_k_mse=False, idx_mode=N.IDX_U8,
+                                                         signs_fp32=False, rnorm_fp32=False, want_vec_norms=True)
+        rows, bits = _ops.pack_mse_qjl(idx, signs, D, self.mse_bits)
+        return {"mse_idx_bytes": rows.reshape(B, H, S, -1), "sign_bits": bits.reshape(B, H, S, D // 8),
+                "vec_norms": vnorm.reshape(B, H, S), "residual_norm": rnorm.reshape(B, H, S), "shape": (B, H, S, D),
+                "packed": True}
+
+    @torch.no_grad()
+    def unpack(self, packed: dict) -> dict:
+        """The reference's dict from the packed form: signs and residual norms exactly, k_mse as
+        fp16((centroids[idx] @ Pi) * vec_norms), which equals compress()'s k_mse up to the rounding of the product."""
+        B, H, S, D = packed["shape"]
+        ipb = 8 // self.mse_bits
+        rows = packed["mse_idx_bytes"].reshape(B * H * S, -1).to(torch.int32)
+        shifts = torch.tensor([self.mse_bits * (ipb - 1 - f) for f in range(ipb)], dtype=torch.int32, device=rows.device)
+        idx = ((rows.unsqueeze(-1) >> shifts) & ((1 << self.mse_bits) - 1)).reshape(B * H * S, -1)[:, :D].to(torch.uint8)
+        sb = packed["sign_bits"].reshape(B * H * S, D // 8).to(torch.int32)
+        bit = (sb.unsqueeze(-1) >> torch.arange(7, -1, -1, dtype=torch.int32, device=sb.device)) & 1
+        signs = (bit.reshape(B * H * S, D) * 2 - 1).to(torch.int8)
+        k32 = torch.empty((1, 1, B * H * S, D), dtype=torch.float32, device=rows.device)
+        job, _keep = _ops.dequantize_job(idx, None, (1, 1, B * H * S, D), self.Pi, self._cb, self.mse_bits, N.IDX_U8, k32)
+        _ops.run_dequantize([job], rows.device)
+        k_mse = (k32.reshape(B * H * S, D) * packed["vec_norms"].reshape(-1, 1)).to(torch.float16)
         return {"k_mse": k_mse.reshape(B, H, S, D), "qjl_signs": signs.reshape(B, H, S, D),
-                "residual_norm": rnorm.reshape(B, H, S), "shape": (B, H, S, D)}
+                "residual_norm": packed["residual_norm"], "shape": (B, H, S, D)}
+
+    @staticmethod
+    def stored_bytes(compressed: dict) -> int:
+        """Bytes of the tensors of a compressed dict (either form)."""
+        return sum(v.numel() * v.element_size() for v in compressed.values() if torch.is_tensor(v))
 
     @torch.no_grad()
     def asymmetric_attention_scores(self, queries: torch.Tensor, compressed: dict) -> torch.Tensor:
+        if compressed.get("packed"):
+            return _ops.qjl_scores_packed(queries, compressed["mse_idx_bytes"], compressed["sign_bits"],
+                                          compressed["vec_norms"], compressed["residual_norm"], self.PiT, self._s_t,
+                                          self._cb, self.mse_bits)
         return _ops.qjl_scores(queries, compressed["k_mse"], compressed["qjl_signs"], compressed["residual_norm"],
                                self._s_t)
 
