@@ -68,8 +68,7 @@ struct Cfg {
   static constexpr uint32_t kOffThr = kOffPi + kPieces * kTileBytes;
   static constexpr uint32_t kThrRegion = 1024;
   static constexpr uint32_t kOffCells = kOffThr + 16384;
-  static constexpr uint32_t kOffThr6 = kOffCells + 16512;
-  static constexpr uint32_t kOffBar = WIDE ? kOffThr6 + 256 : kOffThr + 4 * kThrRegion;
+  static constexpr uint32_t kOffBar = WIDE ? kOffCells + 16512 : kOffThr + 4 * kThrRegion;
   static constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;                // + alignment slack
 };
 static_assert(Cfg<false, true>::kSmemBytes <= 232448 && Cfg<true, true>::kSmemBytes <= 232448, "shared memory budget");
@@ -216,16 +215,16 @@ struct Shortcut {
 // instruction cache while four warps per scheduler run it out of phase.
 // LDS: the candidate's threshold comes from a shared-memory table (thresholds times 2^40) instead of a
 // lane look-up: codes with more than 31 thresholds whose cubic still brackets the index (6 bits).
-// thr_addr is the table's shared address minus 4 * 0x4B000000, so that the look-up address is one
-// multiply-add on the bit pattern of u = 2^23 + e.
+// The table is stored once per lane ([64][32] floats, lane l reads column l: bank l, never a collision).
+// thr_addr is the table's shared address plus 4 * lane minus 128 * 0x4B000000, so that the look-up
+// address is one multiply-add on the bit pattern of u = 2^23 + e.
 template <int BITS, int CH, bool LDS = false, bool LINEAR = false>
-__device__ __forceinline__ void quant_chunk_fast(const uint32_t (&raw)[CH], const Shortcut& sc, uint8_t* dst,
-                                                 bool valid, uint32_t thr_addr = 0u) {
+__device__ __forceinline__ void quant_chunk_words(const uint32_t (&raw)[CH], const Shortcut& sc, uint32_t thr_addr,
+                                                  uint32_t (&acc)[(CH / (8 / BITS)) >= 4 ? (CH / (8 / BITS)) / 4 : 1]) {
   constexpr int IPB = 8 / BITS;
   constexpr int BYTES = CH / IPB;               // packed bytes for CH coordinates
   constexpr int WORDS = BYTES >= 4 ? BYTES / 4 : 1;
   constexpr uint32_t kMagicBits = 0x4B000000u;  // 2^23
-  uint32_t acc[WORDS];
 #pragma unroll
   for (int w = 0; w < WORDS; ++w) acc[w] = 0u;
 #pragma unroll
@@ -247,7 +246,7 @@ __device__ __forceinline__ void quant_chunk_fast(const uint32_t (&raw)[CH], cons
     }
     float thr_h;
     if constexpr (LDS) {
-      asm("ld.shared.f32 %0, [%1];" : "=f"(thr_h) : "r"(__float_as_uint(u) * 4u + thr_addr));
+      asm("ld.shared.f32 %0, [%1];" : "=f"(thr_h) : "r"(__float_as_uint(u) * 128u + thr_addr));
     } else {
       thr_h = __shfl_sync(0xffffffffu, sc.thr_lane_h, __float_as_int(u));
     }
@@ -268,6 +267,29 @@ __device__ __forceinline__ void quant_chunk_fast(const uint32_t (&raw)[CH], cons
     }
     acc[w] -= k;
   }
+}
+
+// Two 16-byte pieces of one row that sit side by side: one 32-byte store when the row allows it.  A warp's store touches 32 different rows either way, so the wider
+// form halves the store traffic through the load/store unit.
+__device__ __forceinline__ void store_index_pair(uint8_t* dst, const uint32_t (&a)[4], const uint32_t (&b)[4], bool wide) {
+  if (wide) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(a[0]), "r"(a[1]), "r"(a[2]),
+                 "r"(a[3]), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3])
+                 : "memory");
+  } else {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(a[0], a[1], a[2], a[3]);
+    *reinterpret_cast<uint4*>(dst + 16) = make_uint4(b[0], b[1], b[2], b[3]);
+  }
+}
+
+template <int BITS, int CH, bool LDS = false, bool LINEAR = false>
+__device__ __forceinline__ void quant_chunk_fast(const uint32_t (&raw)[CH], const Shortcut& sc, uint8_t* dst,
+                                                 bool valid, uint32_t thr_addr = 0u) {
+  constexpr int IPB = 8 / BITS;
+  constexpr int BYTES = CH / IPB;               // packed bytes for CH coordinates
+  constexpr int WORDS = BYTES >= 4 ? BYTES / 4 : 1;
+  uint32_t acc[WORDS];
+  quant_chunk_words<BITS, CH, LDS, LINEAR>(raw, sc, thr_addr, acc);
   if (valid) {
     if constexpr (BYTES == 2) {
       *reinterpret_cast<uint16_t*>(dst) = (uint16_t)acc[0];
@@ -311,13 +333,49 @@ template <int BITS, bool LDS = false, bool LINEAR = false>
 __device__ __forceinline__ void quant_row_fast(uint32_t tacc, uint32_t (&a)[16], uint32_t (&b)[16], const Shortcut& sc,
                                                uint8_t* idx_row, bool valid, uint32_t thr_addr = 0u) {
   constexpr int BYTES = 16 / (8 / BITS);
+  if constexpr (BYTES == 16) {                   // one-byte codes: 32 coordinates leave as one store
+    const bool wide = (reinterpret_cast<uintptr_t>(idx_row) & 31u) == 0;
 #pragma unroll 1
-  for (int c = 0; c < 8; c += 2) {
-    tmem_wait16(a); tmem_issue16(tacc + (c + 1) * 16, b);
-    quant_chunk_fast<BITS, 16, LDS, LINEAR>(a, sc, idx_row + c * BYTES, valid, thr_addr);
-    tmem_wait16(b);
-    if (c + 2 < 8) tmem_issue16(tacc + (c + 2) * 16, a);
-    quant_chunk_fast<BITS, 16, LDS, LINEAR>(b, sc, idx_row + (c + 1) * BYTES, valid, thr_addr);
+    for (int c = 0; c < 8; c += 2) {
+      uint32_t wa[4], wb[4];
+      tmem_wait16(a); tmem_issue16(tacc + (c + 1) * 16, b);
+      quant_chunk_words<BITS, 16, LDS, LINEAR>(a, sc, thr_addr, wa);
+      tmem_wait16(b);
+      if (c + 2 < 8) tmem_issue16(tacc + (c + 2) * 16, a);
+      quant_chunk_words<BITS, 16, LDS, LINEAR>(b, sc, thr_addr, wb);
+      if (valid) store_index_pair(idx_row + c * 16, wa, wb, wide);
+    }
+  } else if constexpr (BYTES == 8) {             // 3- and 4-bit codes: a round (32 coordinates) leaves as one 16-byte store
+#pragma unroll 1
+    for (int c = 0; c < 8; c += 2) {
+      uint32_t wa[2], wb[2];
+      tmem_wait16(a); tmem_issue16(tacc + (c + 1) * 16, b);
+      quant_chunk_words<BITS, 16, LDS, LINEAR>(a, sc, thr_addr, wa);
+      tmem_wait16(b);
+      if (c + 2 < 8) tmem_issue16(tacc + (c + 2) * 16, a);
+      quant_chunk_words<BITS, 16, LDS, LINEAR>(b, sc, thr_addr, wb);
+      if (valid) *reinterpret_cast<uint4*>(idx_row + c * 8) = make_uint4(wa[0], wa[1], wb[0], wb[1]);
+    }
+  } else if constexpr (BYTES == 4) {             // 2-bit codes: a round leaves as one 8-byte store
+#pragma unroll 1
+    for (int c = 0; c < 8; c += 2) {
+      uint32_t wa[1], wb[1];
+      tmem_wait16(a); tmem_issue16(tacc + (c + 1) * 16, b);
+      quant_chunk_words<BITS, 16, LDS, LINEAR>(a, sc, thr_addr, wa);
+      tmem_wait16(b);
+      if (c + 2 < 8) tmem_issue16(tacc + (c + 2) * 16, a);
+      quant_chunk_words<BITS, 16, LDS, LINEAR>(b, sc, thr_addr, wb);
+      if (valid) *reinterpret_cast<uint2*>(idx_row + c * 4) = make_uint2(wa[0], wb[0]);
+    }
+  } else {
+#pragma unroll 1
+    for (int c = 0; c < 8; c += 2) {
+      tmem_wait16(a); tmem_issue16(tacc + (c + 1) * 16, b);
+      quant_chunk_fast<BITS, 16, LDS, LINEAR>(a, sc, idx_row + c * BYTES, valid, thr_addr);
+      tmem_wait16(b);
+      if (c + 2 < 8) tmem_issue16(tacc + (c + 2) * 16, a);
+      quant_chunk_fast<BITS, 16, LDS, LINEAR>(b, sc, idx_row + (c + 1) * BYTES, valid, thr_addr);
+    }
   }
 }
 
@@ -329,8 +387,8 @@ __device__ __forceinline__ void quant_row_fast(uint32_t tacc, uint32_t (&a)[16],
 // cells_lane = table + lane / 2 - 16 * 0x4B000000 (mod 2^32), so that the cell address is one multiply-add
 // on the bit pattern of u = 2^23 + cell;  thr_lane = table + 4 * (lane / 2).
 __device__ __forceinline__ void quant_chunk_cells(const uint32_t (&raw)[16], const Shortcut& sc, uint32_t cells_lane,
-                                                  uint32_t thr_lane, uint8_t* dst, bool valid) {
-  uint32_t acc[4] = {0u, 0u, 0u, 0u};
+                                                  uint32_t thr_lane, uint32_t (&acc)[4]) {
+  acc[0] = acc[1] = acc[2] = acc[3] = 0u;
 #pragma unroll
   for (int e = 0; e < 16; ++e) {
     const float r = __uint_as_float(raw[e]);
@@ -344,18 +402,20 @@ __device__ __forceinline__ void quant_chunk_cells(const uint32_t (&raw)[16], con
     const uint32_t idx = e0 + (__float_as_uint(pf) >> 29);          // pf is 1.0f (0x3F800000) or 0.0f
     acc[e >> 2] = idx * (1u << (8 * (e & 3))) + acc[e >> 2];
   }
-  if (valid) *reinterpret_cast<uint4*>(dst) = make_uint4(acc[0], acc[1], acc[2], acc[3]);
 }
 
 __device__ __forceinline__ void quant_row_cells(uint32_t tacc, uint32_t (&a)[16], uint32_t (&b)[16], const Shortcut& sc,
                                                 uint32_t cells_lane, uint32_t thr_lane, uint8_t* idx_row, bool valid) {
+  const bool wide = (reinterpret_cast<uintptr_t>(idx_row) & 31u) == 0;
 #pragma unroll 1
   for (int c = 0; c < 8; c += 2) {
+    uint32_t wa[4], wb[4];
     tmem_wait16(a); tmem_issue16(tacc + (c + 1) * 16, b);
-    quant_chunk_cells(a, sc, cells_lane, thr_lane, idx_row + c * 16, valid);
+    quant_chunk_cells(a, sc, cells_lane, thr_lane, wa);
     tmem_wait16(b);
     if (c + 2 < 8) tmem_issue16(tacc + (c + 2) * 16, a);
-    quant_chunk_cells(b, sc, cells_lane, thr_lane, idx_row + (c + 1) * 16, valid);
+    quant_chunk_cells(b, sc, cells_lane, thr_lane, wb);
+    if (valid) store_index_pair(idx_row + c * 16, wa, wb, wide);
   }
 }
 
@@ -561,8 +621,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
           uint32_t* cells_rep = reinterpret_cast<uint32_t*>(gbase + C::kOffCells);   // [1025][16 bytes]
           for (int k = ep_tid; k < 1025 * 4; k += 512) cells_rep[k] = (uint32_t)__ldg(cell_e + (k >> 2)) * 0x01010101u;
         } else if (jmode == 1 && jbits == 6) {
-          float* thr6 = reinterpret_cast<float*>(gbase + C::kOffThr6);
-          if (ep_tid < 64) thr6[ep_tid] = __ldg(cb + kThresholdOff + ep_tid) * 1099511627776.0f;
+          float* thr6 = reinterpret_cast<float*>(gbase + C::kOffThr);           // [64][32]
+          for (int k = ep_tid; k < 64 * 32; k += 512) thr6[k] = __ldg(cb + kThresholdOff + (k >> 5)) * 1099511627776.0f;
         }
         asm volatile("bar.sync 5, 512;" ::: "memory");
       }
@@ -621,7 +681,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
                             base + C::kOffThr + 4u * (uint32_t)(lane >> 1), idx_row, valid);
         } else if (WIDE && fast_lds) {
           if constexpr (WIDE)
-            quant_row_fast<6, true>(tacc, ra, rb, sc, idx_row, valid, base + C::kOffThr6 - 4u * 0x4B000000u);
+            quant_row_fast<6, true>(tacc, ra, rb, sc, idx_row, valid, base + C::kOffThr + 4u * (uint32_t)lane - 128u * 0x4B000000u);
         } else if (fast) {
           switch (job.bits) {
             case 1:
@@ -723,7 +783,7 @@ struct DCfg {
   static constexpr uint32_t kOffPi = kOffA + kNA * kPiecesA * kTileBytes;
   static constexpr uint32_t kOffPk = kOffPi + kPiecesB * kTileBytes;
   static constexpr uint32_t kOffStage = kOffPk + kPk * kPkBytes;           // 16-bit outputs: one tile per drain group
-  // 16-bit outputs of wide codes: replicated fp16 look-up table, 256 entries x 32 copies x 2 bytes
+  // 16-bit outputs of wide codes: replicated look-up table (see expand_half_wide16), 16 KB
   static constexpr bool kWide16 = !OUT32 && !NARROW;
   static constexpr uint32_t kOffLut16 = kOffStage + (OUT32 ? 0u : 2u * kTileBytes);
   static constexpr uint32_t kOffBar = kOffLut16 + (kWide16 ? 16384u : 0u);
@@ -987,8 +1047,11 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
     // ---- expanders: 256 threads, one half row each.  A warp whose wait ran out leaves the working
     // loop and walks on for the job-change barriers alone (see the quantize epilogue).
     const int et = threadIdx.x - 64;             // 0..255
-    const int row = et & 127, half = et >> 7;   // a quarter warp = 8 rows of one k-half: conflict-free operand stores
-    const uint32_t lut16_lane = base + C::kOffLut16 + 2u * (uint32_t)lane;
+    // a quarter warp = four consecutive rows x both k-halves: with the chunk order of expand_order() its packed
+    // loads and its operand stores are free of bank conflicts
+    const int row = (et >> 5) * 16 + (lane >> 1), half = lane & 1;
+    const uint32_t lut16_lane = base + C::kOffLut16 + 4u * (uint32_t)lane;          // up to 7 bits: a copy per lane
+    const uint32_t lut16_pair = base + C::kOffLut16 + 4u * (uint32_t)(lane >> 1);   // 8 bits: a copy per lane pair
     bool ok = true;
     DeqJobView job;
     int i = 0;
@@ -1001,11 +1064,17 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
         const __half l = __float2half_rn(c - __half2float(h));
         lut[et] = (uint32_t)__half_as_ushort(h) | ((uint32_t)__half_as_ushort(l) << 16);
         if constexpr (C::kWide16) {
-          if (job.bits >= 5) {                  // 32 copies of entry `et`, two per 32-bit store
+          if (job.bits >= 5) {                  // entry `et` (fp16 bits in both halves): 32 copies, or 16 for 8-bit codes
             const uint32_t hh = (uint32_t)__half_as_ushort(h) * 0x00010001u;
-            uint32_t* copies = reinterpret_cast<uint32_t*>(gbase + C::kOffLut16) + et * 16;
+            if (job.bits == 8) {
+              uint32_t* copies = reinterpret_cast<uint32_t*>(gbase + C::kOffLut16) + et * 16;
 #pragma unroll
-            for (int k = 0; k < 16; ++k) copies[k] = hh;
+              for (int k = 0; k < 16; ++k) copies[k] = hh;
+            } else if (et < 128) {
+              uint32_t* copies = reinterpret_cast<uint32_t*>(gbase + C::kOffLut16) + et * 32;
+#pragma unroll
+              for (int k = 0; k < 32; ++k) copies[(k + lane) & 31] = hh;     // rotated: the warp's stores spread over the banks
+            }
           }
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -1043,7 +1112,7 @@ __global__ void __launch_bounds__(DCfg<OUT32, NARROW>::kThreadsD, 1) k_umma_dequ
             else expand_half<7, C::kPiecesA>(src, lut, a_stage, row, half);
             break;
           default:
-            if constexpr (C::kWide16) expand_half_wide16<8>(src, lut16_lane, a_stage, row, half);
+            if constexpr (C::kWide16) expand_half_wide16<8>(src, lut16_pair, a_stage, row, half);
             else expand_half<8, C::kPiecesA>(src, lut, a_stage, row, half);
             break;
         }
@@ -1207,12 +1276,12 @@ void partition_tiles(const int64_t* tiles, const int* weight, int n_jobs, int gr
 // Cost of a 128-vector tile per code width, in units of 10 ns on one SM at full clocks (measured on
 // (8, 8, 32768, 128) tensors, one width at a time); only the ratios matter.
 int quantize_tile_weight(int bits, bool bf16) {
-  if (bf16) return bits <= 2 ? 142 : bits <= 4 ? 153 : bits == 5 ? 159 : bits == 6 ? 200 : 289;
-  return bits <= 2 ? 120 : bits <= 4 ? 139 : bits == 5 ? 172 : bits == 6 ? 195 : 288;
+  if (bf16) return bits <= 2 ? 139 : bits <= 4 ? 152 : bits == 5 ? 160 : bits == 6 ? 188 : 290;
+  return bits <= 2 ? 120 : bits <= 4 ? 137 : bits == 5 ? 175 : bits == 6 ? 183 : 290;
 }
 int dequantize_tile_weight(int bits, bool out32) {
   if (out32) return bits <= 4 ? 250 : 300;
-  return bits <= 2 ? 128 : bits <= 4 ? 140 : 211;
+  return bits <= 2 ? 127 : bits <= 4 ? 131 : bits <= 7 ? 146 : 163;
 }
 
 }  // namespace
