@@ -103,7 +103,9 @@ def rank_layers(cfg, rank: int, world: int):
 class ClockSampler:
     """Polls NVML (read only) for SM clock and throttle reasons while the measured regions run."""
 
-    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+               0x2: "applications_clocks_setting", 0x10: "sync_boost", 0x80: "hw_power_brake_slowdown",
+               0x100: "display_clock_setting"}
 
     def __init__(self, index: int):
         self.samples, self.reasons, self.max_mhz = [], set(), None

@@ -55,20 +55,22 @@ constexpr int kMaxCtas = 192;                          // upper bound of the gri
 // shared memory map (offsets from a 1024-byte aligned base)
 template <bool BF16, bool WIDE = false>
 struct Cfg {
-  static constexpr int kStages = BF16 ? 3 : 4;
+  // x-tile ring: launches with wide codes give one stage to the look-up tables (their tiles take 1.7-2.5 us,
+  // enough for a load to land with one tile of look-ahead less)
+  static constexpr int kStages = (BF16 ? 3 : 4) - (WIDE ? 1 : 0);
   static constexpr int kPieces = BF16 ? 3 : 2;
   static constexpr uint32_t kPieceOff = BF16 ? 2 * kTileBytes : 0;            // offset of the pieces in the image
   static constexpr uint32_t kOffA = 0;
   static constexpr uint32_t kOffPi = kOffA + kStages * kTileBytes;
   // Narrow launches: 256 thresholds (fp32) per epilogue warpgroup.  Launches with wide codes: ONE set of
-  // tables per CTA, shared by the four warpgroups and rebuilt at every job change (see the epilogue):
-  //   thresholds * 2^40 of 7/8-bit codes, 16 copies each (copy = lane / 2): 256 x 64 bytes,
-  //   candidate index per cell of t, 16 byte copies each:                    1025 x 16 bytes,
-  //   thresholds * 2^40 of 6-bit codes (one copy):                            64 x 4 bytes
+  // tables per CTA, shared by the four warpgroups and rebuilt at every job change (see the epilogue), every
+  // entry stored once per lane so that random look-ups never collide in the banks:
+  //   thresholds * 2^40 of 7/8-bit codes:        256 x 32 x 4 bytes   (6-bit codes: 64 x 32 x 4 bytes, same place),
+  //   candidate index per cell of t (7/8 bits): 1025 x 32 x 1 byte    (four lanes share a word)
   static constexpr uint32_t kOffThr = kOffPi + kPieces * kTileBytes;
   static constexpr uint32_t kThrRegion = 1024;
-  static constexpr uint32_t kOffCells = kOffThr + 16384;
-  static constexpr uint32_t kOffBar = WIDE ? kOffCells + 16512 : kOffThr + 4 * kThrRegion;
+  static constexpr uint32_t kOffCells = kOffThr + 32768;
+  static constexpr uint32_t kOffBar = WIDE ? kOffCells + 32800 : kOffThr + 4 * kThrRegion;
   static constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;                // + alignment slack
 };
 static_assert(Cfg<false, true>::kSmemBytes <= 232448 && Cfg<true, true>::kSmemBytes <= 232448, "shared memory budget");
@@ -382,10 +384,10 @@ __device__ __forceinline__ void quant_row_fast(uint32_t tacc, uint32_t (&a)[16],
 // 7- and 8-bit codes (one index per byte): the candidate e comes from a byte table over the 1024 uniform
 // cells of t, its threshold (times 2^40) from a second table, then the saturating-fma compare.  Random
 // look-ups by 32 lanes cost a shared-memory wavefront per bank collision, and these two were the whole
-// cost of the wide codes, so both tables are stored 16 times and lane l reads copy l / 2: a threshold
-// look-up can only collide inside a lane pair, a cell look-up inside a group of eight lanes.
-// cells_lane = table + lane / 2 - 16 * 0x4B000000 (mod 2^32), so that the cell address is one multiply-add
-// on the bit pattern of u = 2^23 + cell;  thr_lane = table + 4 * (lane / 2).
+// cost of the wide codes, so both tables are stored once per lane: a threshold look-up never collides
+// (lane l reads bank l), a cell look-up only inside a group of four lanes that share a 32-bit word.
+// cells_lane = table + lane - 32 * 0x4B000000 (mod 2^32), so that the cell address is one multiply-add
+// on the bit pattern of u = 2^23 + cell;  thr_lane = table + 4 * lane.
 __device__ __forceinline__ void quant_chunk_cells(const uint32_t (&raw)[16], const Shortcut& sc, uint32_t cells_lane,
                                                   uint32_t thr_lane, uint32_t (&acc)[4]) {
   acc[0] = acc[1] = acc[2] = acc[3] = 0u;
@@ -396,8 +398,8 @@ __device__ __forceinline__ void quant_chunk_cells(const uint32_t (&raw)[16], con
     uint32_t e0;
     asm("fma.rn.sat.f32 %0, %1, %2, 0f3F000000;" : "=f"(t) : "f"(r), "f"(sc.s_inv));
     const float u = fmaf(t, 1024.0f, 8388608.0f);
-    asm("ld.shared.u8 %0, [%1];" : "=r"(e0) : "r"(__float_as_uint(u) * 16u + cells_lane));
-    asm("ld.shared.f32 %0, [%1];" : "=f"(thr_h) : "r"(e0 * 64u + thr_lane));
+    asm("ld.shared.u8 %0, [%1];" : "=r"(e0) : "r"(__float_as_uint(u) * 32u + cells_lane));
+    asm("ld.shared.f32 %0, [%1];" : "=f"(thr_h) : "r"(e0 * 128u + thr_lane));
     asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(pf) : "f"(r), "f"(sc.h_inv), "f"(-thr_h));
     const uint32_t idx = e0 + (__float_as_uint(pf) >> 29);          // pf is 1.0f (0x3F800000) or 0.0f
     acc[e >> 2] = idx * (1u << (8 * (e & 3))) + acc[e >> 2];
@@ -615,11 +617,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
         const int jbits = batch.jobs[seq_job].bits;
         const int jmode = (int)__ldg(cb + 512);
         if (jmode == 2 && jbits >= 5) {
-          float* thr_rep = reinterpret_cast<float*>(gbase + C::kOffThr);        // [256][16]
-          for (int k = ep_tid; k < 256 * 16; k += 512) thr_rep[k] = __ldg(cb + kThresholdOff + (k >> 4)) * 1099511627776.0f;
+          float* thr_rep = reinterpret_cast<float*>(gbase + C::kOffThr);        // [256][32]
+          for (int k = ep_tid; k < 256 * 32; k += 512) thr_rep[k] = __ldg(cb + kThresholdOff + (k >> 5)) * 1099511627776.0f;
           const uint8_t* cell_e = reinterpret_cast<const uint8_t*>(cb + 528);
-          uint32_t* cells_rep = reinterpret_cast<uint32_t*>(gbase + C::kOffCells);   // [1025][16 bytes]
-          for (int k = ep_tid; k < 1025 * 4; k += 512) cells_rep[k] = (uint32_t)__ldg(cell_e + (k >> 2)) * 0x01010101u;
+          uint32_t* cells_rep = reinterpret_cast<uint32_t*>(gbase + C::kOffCells);   // [1025][32 bytes]
+          for (int k = ep_tid; k < 1025 * 8; k += 512) cells_rep[k] = (uint32_t)__ldg(cell_e + (k >> 3)) * 0x01010101u;
         } else if (jmode == 1 && jbits == 6) {
           float* thr6 = reinterpret_cast<float*>(gbase + C::kOffThr);           // [64][32]
           for (int k = ep_tid; k < 64 * 32; k += 512) thr6[k] = __ldg(cb + kThresholdOff + (k >> 5)) * 1099511627776.0f;
@@ -677,8 +679,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_quantize(const __grid_cons
           tmem_wait16(ra);
         } else if (WIDE && mode == 2) {
           if constexpr (WIDE)
-            quant_row_cells(tacc, ra, rb, sc, base + C::kOffCells + (uint32_t)(lane >> 1) - 16u * 0x4B000000u,
-                            base + C::kOffThr + 4u * (uint32_t)(lane >> 1), idx_row, valid);
+            quant_row_cells(tacc, ra, rb, sc, base + C::kOffCells + (uint32_t)lane - 32u * 0x4B000000u,
+                            base + C::kOffThr + 4u * (uint32_t)lane, idx_row, valid);
         } else if (WIDE && fast_lds) {
           if constexpr (WIDE)
             quant_row_fast<6, true>(tacc, ra, rb, sc, idx_row, valid, base + C::kOffThr + 4u * (uint32_t)lane - 128u * 0x4B000000u);
@@ -1276,8 +1278,8 @@ void partition_tiles(const int64_t* tiles, const int* weight, int n_jobs, int gr
 // Cost of a 128-vector tile per code width, in units of 10 ns on one SM at full clocks (measured on
 // (8, 8, 32768, 128) tensors, one width at a time); only the ratios matter.
 int quantize_tile_weight(int bits, bool bf16) {
-  if (bf16) return bits <= 2 ? 139 : bits <= 4 ? 152 : bits == 5 ? 160 : bits == 6 ? 188 : 290;
-  return bits <= 2 ? 120 : bits <= 4 ? 137 : bits == 5 ? 175 : bits == 6 ? 183 : 290;
+  if (bf16) return bits <= 2 ? 140 : bits <= 5 ? 152 : bits == 6 ? 170 : 207;
+  return bits <= 2 ? 117 : bits <= 4 ? 137 : bits == 5 ? 146 : bits == 6 ? 163 : 203;
 }
 int dequantize_tile_weight(int bits, bool out32) {
   if (out32) return bits <= 4 ? 250 : 300;
