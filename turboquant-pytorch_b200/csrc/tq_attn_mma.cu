@@ -18,6 +18,8 @@
 //     (all four cross terms), one shuffle away.
 // The softmax partials per block of keys and the finishing pass are those of the FP32 path.
 
+#include <atomic>
+
 #include "tq_common.cuh"
 #include "tq_internal.h"
 
@@ -581,16 +583,30 @@ __global__ void __launch_bounds__(128) k_decode_finish(FinishParams F) {
   __syncthreads();
   // rotated-domain accumulator and sum of the packed part; thread = coordinate
   float acc = 0.f, lsum = 0.f;
-  if (F.Sk > 0)
-    for (int i = 0; i < F.nblk; ++i) {
-      const float* pp = F.part + (row * F.nblk + i) * kPartStride;
-      const float pm = pp[0];
-      if (pm != -INFINITY) {
-        const float f = __expf(pm - m);
-        acc += pp[2 + tid] * f;
-        lsum += pp[1] * f;
+  if (F.Sk > 0) {
+    // eight partials per round: their loads are independent and in flight together (a loop that tests each
+    // partial's maximum before loading the next spends one memory latency per partial)
+    constexpr int kBatch = 8;
+    for (int i0 = 0; i0 < F.nblk; i0 += kBatch) {
+      float pm[kBatch], ps[kBatch], pv[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int i = i0 + u < F.nblk ? i0 + u : F.nblk - 1;
+        const float* pp = F.part + (row * F.nblk + i) * kPartStride;
+        pm[u] = i0 + u < F.nblk ? pp[0] : -INFINITY;
+        ps[u] = pp[1];
+        pv[u] = pp[2 + tid];
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        if (pm[u] != -INFINITY) {
+          const float f = __expf(pm[u] - m);
+          acc += pv[u] * f;
+          lsum += ps[u] * f;
+        }
       }
     }
+  }
   sh_acc[tid] = acc;
   // window probabilities
   float wl = 0.f;
@@ -605,6 +621,7 @@ __global__ void __launch_bounds__(128) k_decode_finish(FinishParams F) {
   const float total = lsum + sh_red[0] + sh_red[1] + sh_red[2] + sh_red[3];
   // out[tid] = sum_j acc[j] Pi_v[j][tid] + sum_w p_w v_w[tid]
   float o = 0.f;
+#pragma unroll 16
   for (int j = 0; j < kDimA; ++j) o = fmaf(sh_acc[j], __ldg(F.v_rotation + j * kDimA + tid), o);
   for (int64_t w = 0; w < F.W; ++w) o = fmaf(sh_w[w], load_elem<WDT>(F.v_window, wbase + w * F.ws_s + tid), o);
   F.out[row * kDimA + tid] = o / total;
@@ -635,8 +652,34 @@ static int launch_decode_v(const DecodeParams& P, int vbits, unsigned blocks, cu
   return check_launch();
 }
 
+// Keys per CTA such that the CTAs fill whole waves of `slots` resident CTAs: at least min_keys (the scratch is
+// sized for blocks of min_keys), a multiple of 16.  With 8 KV heads and 131 072 keys, blocks of 2048 keys are
+// 512 CTAs = 3.46 waves of 148, i.e. four rounds of which the last is half empty; 55 blocks of 2384 keys per head
+// are 2.97 waves.
+static int wave_keys_per_block(int64_t units, int64_t Sk, int min_keys, int slots) {
+  const int64_t nblk_max = (Sk + min_keys - 1) / min_keys;
+  if (units <= 0 || slots <= 0 || units * nblk_max <= slots) return min_keys;
+  const int64_t waves = units * nblk_max / slots;
+  int64_t nblk = waves * slots / units;
+  if (nblk < 1) nblk = 1;
+  int64_t kpb = (Sk + nblk - 1) / nblk;
+  kpb = (kpb + 15) / 16 * 16;
+  return (int)(kpb < min_keys ? min_keys : kpb);
+}
+
+static int device_sm_count() {
+  static std::atomic<int> cached[64] = {};
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev >= 0 && dev < 64 && (n = cached[dev].load()) > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+  if (dev >= 0 && dev < 64) cached[dev].store(n);
+  return n;
+}
+
 int decode_attention(const TqDecodeAttnJob& job, cudaStream_t st) {
-  constexpr int kKeysPerBlock = 2048;
+  constexpr int kMinKeysPerBlock = 2048;          // decode_attention_workspace() sizes the partials for this
+  const int kKeysPerBlock = wave_keys_per_block(job.B * job.Hkv, job.Sk, kMinKeysPerBlock, device_sm_count());
   const int64_t rows = job.B * job.Hq * job.Sq;
   const int nblk = job.Sk > 0 ? (int)((job.Sk + kKeysPerBlock - 1) / kKeysPerBlock) : 1;
   float* qrot = reinterpret_cast<float*>(job.workspace);
@@ -696,6 +739,10 @@ bool mma_score_eligible(const TqScoreJob& job) {
 }
 
 // logits (and the per-block softmax partials when stats != NULL) for a job whose queries are already rotated
+int mma_score_keys_per_block(const TqScoreJob& job, int min_keys) {
+  return wave_keys_per_block(job.B * job.Hkv, job.Sk, min_keys, 2 * device_sm_count());      // two CTAs per SM
+}
+
 int mma_score_packed(const TqScoreJob& job, const float* qrot, float* stats, int nblk, int keys_per_block, cudaStream_t st) {
   const int64_t blocks = job.B * job.Hkv * nblk;
   switch (job.bits) {

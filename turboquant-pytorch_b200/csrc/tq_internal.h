@@ -35,6 +35,8 @@ int simt_prod_inner_product(const float* y, int64_t ny, const int64_t* idx, cons
 // packed-key logits on the tensor cores, mma.sync (tq_attn_mma.cu); queries already rotated
 bool mma_score_eligible(const TqScoreJob& job);
 int mma_score_packed(const TqScoreJob& job, const float* qrot, float* stats, int nblk, int keys_per_block, cudaStream_t st);
+// keys per CTA (>= min_keys, for which the caller's scratch is sized) that makes the CTAs fill whole waves
+int mma_score_keys_per_block(const TqScoreJob& job, int min_keys);
 
 // decode attention on packed keys and packed values (tq_attn_mma.cu)
 size_t decode_attention_workspace(int64_t B, int64_t Hq, int64_t Sq, int64_t Sk, int keys_per_block);

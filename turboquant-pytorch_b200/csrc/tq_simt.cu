@@ -1034,7 +1034,11 @@ size_t simt_score_workspace(int64_t B, int64_t Hq, int64_t Sq, int64_t Sk, int D
 int simt_score_packed(const TqScoreJob& job, cudaStream_t st) {
   const int64_t rows = job.B * job.Hq * job.Sq;
   if (rows == 0 || job.Sk == 0) return TQ_OK;
-  const int nblk = (int)((job.Sk + SCORE_KEYS_PER_BLOCK - 1) / SCORE_KEYS_PER_BLOCK);
+  // the tensor-core kernel takes its block size as a parameter: blocks of at least SCORE_KEYS_PER_BLOCK keys (the
+  // scratch is sized for that) chosen so that the CTAs fill whole waves
+  const bool use_mma = mma_score_eligible(job);
+  const int kpb = use_mma ? mma_score_keys_per_block(job, SCORE_KEYS_PER_BLOCK) : SCORE_KEYS_PER_BLOCK;
+  const int nblk = (int)((job.Sk + kpb - 1) / kpb);
   float* qrot = reinterpret_cast<float*>(job.workspace);
   size_t qbytes = ((size_t)rows * job.D * sizeof(float) + 255) / 256 * 256;
   float* stats = reinterpret_cast<float*>(reinterpret_cast<char*>(job.workspace) + qbytes);
@@ -1042,8 +1046,8 @@ int simt_score_packed(const TqScoreJob& job, cudaStream_t st) {
   if (rc != TQ_OK) return rc;
   const int64_t blocks = job.B * job.Hkv * nblk;
   float* st_ptr = job.probs != nullptr ? stats : nullptr;
-  if (mma_score_eligible(job)) {
-    rc = mma_score_packed(job, qrot, st_ptr, nblk, SCORE_KEYS_PER_BLOCK, st);
+  if (use_mma) {
+    rc = mma_score_packed(job, qrot, st_ptr, nblk, kpb, st);
     if (rc != TQ_OK) return rc;
   } else if (job.D == 128 && ((uintptr_t)job.idx_bytes & 15u) == 0) {
     switch (job.bits) {
@@ -1059,7 +1063,7 @@ int simt_score_packed(const TqScoreJob& job, cudaStream_t st) {
   } else {
     k_score_packed<<<(unsigned)blocks, NT, 0, st>>>(job, qrot, st_ptr, nblk);
   }
-  if (!mma_score_eligible(job)) rc = check_launch();
+  if (!use_mma) rc = check_launch();
   if (rc != TQ_OK || job.probs == nullptr) return rc;
   int chunks = (int)((job.Sk + 4095) / 4096);
   dim3 grid((unsigned)rows, (unsigned)chunks);
