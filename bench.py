@@ -561,9 +561,21 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         import torch.distributed as dist
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"          # keeps NCCL's version banner off stdout (one JSON line only)
-        dist.init_process_group("nccl", device_id=dev)
+        # NCCL prints its version banner on stdout when NCCL_DEBUG (environment or nccl.conf) asks for it; stdout
+        # carries ONE JSON line, so the communicator is created with file descriptor 1 pointing at stderr
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev)
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
     lib = _native.lib()
     refuse_profiling_switches(lib)
     if args.workload not in CACHES:
