@@ -292,7 +292,12 @@ typedef struct {
   const float* codebook;
   const float* qjl_t;     /* [dev] S^T, (D, M) row-major fp32: projected = residual @ qjl_t   */
   int32_t M;              /* QJL projection width, 1..256                                     */
-  int32_t signs_dtype;    /* 0: int8 +-1 with >=0 -> +1; 1: fp32 +-1 with 0 -> +1             */
+  int32_t signs_dtype;    /* 0: int8 +-1 with >=0 -> +1; 1: fp32 +-1 with 0 -> +1;
+                             2: one bit per sign, (N, M / 8) bytes, coordinate j in bit 7 - j % 8 of byte j / 8, set for
+                             +1 (the form tq_qjl_scores_packed reads).  2, and idx_mode TQ_IDX_PACKED for idx_out
+                             (bit-packed rows as tq_quantize writes them), are served by the tensor-core path only:
+                             a job that asks for them and does not qualify for it returns TQ_EINVAL (write the unpacked
+                             forms and call tq_pack_mse_qjl instead)                            */
   int32_t rnorm_dtype;    /* TQ_F16 | TQ_F32                                                  */
   int32_t idx_mode;       /* layout of idx_out when it is not NULL                            */
   uint16_t* k_mse_out;    /* [dev] fp16 (N, D) or NULL                                        */

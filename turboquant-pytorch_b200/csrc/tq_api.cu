@@ -454,13 +454,16 @@ int tq_qjl_compress(const TqQjlCompressJob* job, void* stream) {
   if (job->M < 1 || job->M > TQ_MAX_DIM) return TQ_EDIM;
   if (bad_dtype(job->x_dtype)) return TQ_EDTYPE;
   if (job->rnorm_dtype != TQ_F16 && job->rnorm_dtype != TQ_F32) return TQ_EDTYPE;
-  if (job->B < 0 || job->H < 0 || job->S < 0 || (job->signs_dtype != 0 && job->signs_dtype != 1)) return TQ_EINVAL;
-  if (job->idx_out != nullptr && job->idx_mode != TQ_IDX_U8 && job->idx_mode != TQ_IDX_I64) return TQ_EINVAL;
+  if (job->B < 0 || job->H < 0 || job->S < 0 || job->signs_dtype < 0 || job->signs_dtype > 2) return TQ_EINVAL;
+  const bool packed_idx = job->idx_out != nullptr && job->idx_mode == TQ_IDX_PACKED;
+  if (job->idx_out != nullptr && job->idx_mode != TQ_IDX_U8 && job->idx_mode != TQ_IDX_I64 && !packed_idx) return TQ_EINVAL;
+  const bool packed_outputs = packed_idx || job->signs_dtype == 2;
   if (job->B * job->H * job->S == 0) return TQ_OK;
   if (job->x == nullptr || job->rotation_t == nullptr || job->rotation == nullptr || job->codebook == nullptr ||
       job->qjl_t == nullptr || job->signs_out == nullptr || job->rnorm_out == nullptr)
     return TQ_ENULL;
   if (tq::umma_v2_compress_eligible(*job)) return tq::umma_v2_compress(*job, (cudaStream_t)stream);
+  if (packed_outputs) return TQ_EINVAL;      // packed outputs are written by the tensor-core path only
   return tq::simt_qjl_compress(*job, (cudaStream_t)stream);
 }
 

@@ -63,6 +63,8 @@ struct V2Stage {
   uint16_t* p_lo;
   float* norms;              // scratch (n): ||x||
   uint8_t* idx_u8_out;       // stage 1: optional, one index per byte (n, D)
+  uint8_t* idx_packed_out;   // stage 1: optional, bit-packed rows (n, G), first index in the high bits
+  uint8_t* sign_bits_out;    // stage 3: optional, one bit per sign (n, D / 8), coordinate j in bit 7 - j % 8, set for +1
   uint16_t* k_mse_out;       // stage 2: optional
   uint16_t* rnorm_out;       // stage 2, fp16 bits
   int8_t* signs_out;         // stage 3
@@ -340,6 +342,37 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
           }
           if (valid && p.idx_u8_out != nullptr)
             *reinterpret_cast<uint4*>(p.idx_u8_out + row * D + col0 + c * 16) = make_uint4(ib[0], ib[1], ib[2], ib[3]);
+          if (valid && p.idx_packed_out != nullptr) {
+            // the 16 indices of this step as 16 / ipb packed bytes of the row
+            const int ipb = 8 / bits;
+            uint8_t* dst = p.idx_packed_out + row * (int64_t)(D / ipb) + (col0 + c * 16) / ipb;
+            if (ipb == 1) {
+              *reinterpret_cast<uint4*>(dst) = make_uint4(ib[0], ib[1], ib[2], ib[3]);
+            } else if (ipb == 2) {           // 3- and 4-bit codes: byte k = idx[2k] << bits | idx[2k+1]
+              uint32_t o[2];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const uint32_t a = ib[2 * h], b = ib[2 * h + 1];
+                const uint32_t b0 = (((a >> 0) & 0xFFu) << bits) | ((a >> 8) & 0xFFu), b1 = (((a >> 16) & 0xFFu) << bits) | (a >> 24);
+                const uint32_t b2 = (((b >> 0) & 0xFFu) << bits) | ((b >> 8) & 0xFFu), b3 = (((b >> 16) & 0xFFu) << bits) | (b >> 24);
+                o[h] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+              }
+              *reinterpret_cast<uint2*>(dst) = make_uint2(o[0], o[1]);
+            } else if (ipb == 4) {           // 2-bit codes
+              uint32_t o = 0u;
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const uint32_t a = ib[k];
+                o |= ((((a >> 0) & 3u) << 6) | (((a >> 8) & 3u) << 4) | (((a >> 16) & 3u) << 2) | ((a >> 24) & 3u)) << (8 * k);
+              }
+              *reinterpret_cast<uint32_t*>(dst) = o;
+            } else {                          // 1-bit codes
+              uint32_t o = 0u;
+#pragma unroll
+              for (int e = 0; e < 16; ++e) o |= ((ib[e >> 2] >> (8 * (e & 3))) & 1u) << (8 * (e >> 3) + 7 - (e & 7));
+              *reinterpret_cast<uint16_t*>(dst) = (uint16_t)o;
+            }
+          }
           if (valid) {
             uint32_t ph[8], pl[8];
 #pragma unroll
@@ -403,7 +436,7 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
 #pragma unroll 1
         for (int c = 0; c < 8; ++c) {
           tmem_ld16(tacc + c * 16, v);
-          if (valid) {
+          if (valid && p.signs_out != nullptr) {
             uint32_t sw[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -416,6 +449,12 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
               sw[j] = x;
             }
             *reinterpret_cast<uint4*>(p.signs_out + row * D + col0 + c * 16) = make_uint4(sw[0], sw[1], sw[2], sw[3]);
+          }
+          if (valid && p.sign_bits_out != nullptr) {
+            uint32_t o = 0u;
+#pragma unroll
+            for (int e = 0; e < 16; ++e) o |= (__uint_as_float(v[e]) >= 0.f ? 1u : 0u) << (8 * (e >> 3) + 7 - (e & 7));
+            *reinterpret_cast<uint16_t*>(p.sign_bits_out + row * (D / 8) + (col0 + c * 16) / 8) = (uint16_t)o;
           }
         }
       }
@@ -489,10 +528,12 @@ int run(const TqQjlCompressJob& job, cudaStream_t st) {
   p.p_hi = p_hi;
   p.p_lo = p_lo;
   p.norms = job.vec_norms_out != nullptr ? job.vec_norms_out : norms;
-  p.idx_u8_out = reinterpret_cast<uint8_t*>(job.idx_out);
+  p.idx_u8_out = job.idx_mode == TQ_IDX_PACKED ? nullptr : reinterpret_cast<uint8_t*>(job.idx_out);
+  p.idx_packed_out = job.idx_mode == TQ_IDX_PACKED ? reinterpret_cast<uint8_t*>(job.idx_out) : nullptr;
   p.k_mse_out = job.k_mse_out;
   p.rnorm_out = reinterpret_cast<uint16_t*>(job.rnorm_out);
-  p.signs_out = reinterpret_cast<int8_t*>(job.signs_out);
+  p.signs_out = job.signs_dtype == 2 ? nullptr : reinterpret_cast<int8_t*>(job.signs_out);
+  p.sign_bits_out = job.signs_dtype == 2 ? reinterpret_cast<uint8_t*>(job.signs_out) : nullptr;
   p.n = n;
   p.tiles = (int32_t)tiles;
   p.bits = job.bits;
@@ -526,8 +567,9 @@ size_t umma_v2_compress_workspace(int64_t n, int D) {
 bool umma_v2_compress_eligible(const TqQjlCompressJob& job) {
   if (force_simt()) return false;
   if (job.D != 128 && job.D != 256) return false;
-  if (job.x_dtype != TQ_F16 || job.normalize != 1 || job.signs_dtype != 0 || job.rnorm_dtype != TQ_F16) return false;
-  if (job.M != job.D || (job.idx_out != nullptr && job.idx_mode != TQ_IDX_U8)) return false;
+  if (job.x_dtype != TQ_F16 || job.normalize != 1 || (job.signs_dtype != 0 && job.signs_dtype != 2) || job.rnorm_dtype != TQ_F16)
+    return false;
+  if (job.M != job.D || (job.idx_out != nullptr && job.idx_mode != TQ_IDX_U8 && job.idx_mode != TQ_IDX_PACKED)) return false;
   if (job.bits < 1 || job.bits > 8) return false;
   const int64_t n = job.B * job.H * job.S;
   if (n <= 0) return false;

@@ -19,6 +19,7 @@ LIB_PATH = os.environ.get("TURBOQUANT_B200_LIB") or os.path.join(_HERE, "libturb
 
 F32, F16, BF16 = 0, 1, 2
 IDX_PACKED, IDX_U8, IDX_I64 = 0, 1, 2
+EINVAL = -1                      # TQ_EINVAL
 CODEBOOK_FLOATS = 800
 SCORE_NOALLOC_SCRATCH_BYTES = 4 << 20
 

@@ -273,6 +273,42 @@ def qjl_compress(x: torch.Tensor, pi: torch.Tensor, pi_t: torch.Tensor, codebook
     return k_mse, idx, signs, rnorm
 
 
+def qjl_compress_packed(x: torch.Tensor, pi: torch.Tensor, pi_t: torch.Tensor, codebook: torch.Tensor,
+                        qjl_t: torch.Tensor, bits: int):
+    """MSE stage + QJL signs of a (B,H,S,D) tensor straight into the packed form: returns (index rows (n, G) uint8,
+    sign bits (n, D/8) uint8, residual norms (n,) fp16, vector norms (n,) fp32).  The tensor-core path writes the packed
+    rows from its epilogues; inputs it does not take go through the unpacked outputs and tq_pack_mse_qjl."""
+    N.require_cuda(x, "qjl_compress")
+    B, H, S, D = x.shape
+    n = B * H * S
+    dev = x.device
+    L = N.lib()
+    if x.dtype == torch.float16 and x.is_contiguous() and D in (128, 256) and qjl_t.shape[1] == D and n > 0:
+        ws_bytes = L.tq_qjl_compress_workspace_bytes(n, D)
+        if ws_bytes:
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+            rows = torch.empty((n, N.packed_row_bytes(D, bits)), dtype=torch.uint8, device=dev)
+            sbits = torch.empty((n, D // 8), dtype=torch.uint8, device=dev)
+            rnorm = torch.empty((n,), dtype=torch.float16, device=dev)
+            vnorm = torch.empty((n,), dtype=torch.float32, device=dev)
+            job = N.QjlCompressJob(x=x.data_ptr(), x_dtype=N.dtype_code(x), D=D, bits=bits, normalize=1, B=B, H=H, S=S,
+                                   stride_b=H * S * D, stride_h=S * D, stride_s=D, rotation_t=pi_t.data_ptr(),
+                                   rotation=pi.data_ptr(), codebook=codebook.data_ptr(), qjl_t=qjl_t.data_ptr(), M=D,
+                                   signs_dtype=2, rnorm_dtype=N.F16, idx_mode=N.IDX_PACKED, k_mse_out=None,
+                                   idx_out=rows.data_ptr(), signs_out=sbits.data_ptr(), rnorm_out=rnorm.data_ptr(),
+                                   workspace=ws.data_ptr(), workspace_bytes=ws_bytes, vec_norms_out=vnorm.data_ptr())
+            with torch.cuda.device(dev):
+                rc = L.tq_qjl_compress(C.byref(job), N.stream_ptr(dev))
+            if rc == 0:
+                return rows, sbits, rnorm, vnorm
+            if rc != N.EINVAL:
+                N.check(rc, "tq_qjl_compress")
+    _k, idx, signs, rnorm, vnorm = qjl_compress(x, pi, pi_t, codebook, qjl_t, bits, normalize=True, want_k_mse=False,
+                                                idx_mode=N.IDX_U8, signs_fp32=False, rnorm_fp32=False, want_vec_norms=True)
+    rows, sbits = pack_mse_qjl(idx, signs, D, bits)
+    return rows, sbits, rnorm, vnorm
+
+
 def pack_mse_qjl(idx_u8: Optional[torch.Tensor], signs_i8: Optional[torch.Tensor], D: int, bits: int):
     """(n, D) uint8 indices and (n, D) int8 signs -> (packed index rows (n, G) | None, sign bits (n, D/8) | None)."""
     src = idx_u8 if idx_u8 is not None else signs_i8

@@ -48,10 +48,7 @@ class TurboQuantCompressorV2:
                     "residual_norm": rnorm.reshape(B, H, S), "shape": (B, H, S, D)}
         if D % 8:
             raise ValueError("packed=True needs head_dim to be a multiple of 8")
-        _k, idx, signs, rnorm, vnorm = _ops.qjl_compress(states, self.Pi, self.PiT, self._cb, self._s_t, self.mse_bits,
-                                                         normalize=True, want_k_mse=False, idx_mode=N.IDX_U8,
-                                                         signs_fp32=False, rnorm_fp32=False, want_vec_norms=True)
-        rows, bits = _ops.pack_mse_qjl(idx, signs, D, self.mse_bits)
+        rows, bits, rnorm, vnorm = _ops.qjl_compress_packed(states, self.Pi, self.PiT, self._cb, self._s_t, self.mse_bits)
         return {"mse_idx_bytes": rows.reshape(B, H, S, -1), "sign_bits": bits.reshape(B, H, S, D // 8),
                 "vec_norms": vnorm.reshape(B, H, S), "residual_norm": rnorm.reshape(B, H, S), "shape": (B, H, S, D),
                 "packed": True}
