@@ -50,7 +50,7 @@ CACHES = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per 128-vector tile of the dominant kernel, from ncu captures of a
 # smaller case of the same launch (the summaries name the commands); traffic grows in proportion to the tiles.
-NCU_DRAM_BYTES_PER_VECTOR = {("kv", "quantize"): 351.8, ("kv", "dequantize"): 335.1}
+NCU_DRAM_BYTES_PER_VECTOR = {("kv", "quantize"): 348.3, ("kv", "dequantize"): 333.6}
 
 
 def packed_row_bytes(bits: int) -> int:
