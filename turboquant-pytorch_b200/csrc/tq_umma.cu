@@ -207,6 +207,21 @@ __device__ __noinline__ void quant_row_search(int bits, uint32_t tacc, float inv
 // threshold, one compare.  Arithmetic is kept on the FMA pipe: the index is built as a
 // float next to 2^23 and shifted into the packed word by an integer multiply-add; the
 // 2^23 bit patterns that ride along are removed once per word as a constant.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+  unsigned long long v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// two fp32 fused multiply-adds in one instruction (sm_100): the same IEEE results per half as fmaf
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
 struct Shortcut {
   float s, c1, c2, c3;
   float thr_lane_h;    // threshold[lane] * 2^40 (+inf past the last one)
@@ -305,30 +320,33 @@ __device__ __forceinline__ void quant_chunk_fast(const uint32_t (&raw)[CH], cons
   }
 }
 
+// sum of squares on packed pairs: even coordinates accumulate in the low half, odd ones in the high half
 template <int CH>
-__device__ __forceinline__ float ssq_chunk(const uint32_t (&raw)[CH], float ssq) {
+__device__ __forceinline__ unsigned long long ssq_chunk(const uint32_t (&raw)[CH], unsigned long long ssq2) {
 #pragma unroll
-  for (int e = 0; e < CH; ++e) {
-    const float v = __uint_as_float(raw[e]);
-    ssq = fmaf(v, v, ssq);
+  for (int e = 0; e < CH; e += 2) {
+    const unsigned long long v = pack2(__uint_as_float(raw[e]), __uint_as_float(raw[e + 1]));
+    ssq2 = fma2(v, v, ssq2);
   }
-  return ssq;
+  return ssq2;
 }
 
 // A thread owns one vector: eight 16-column steps per sweep.  Two register buffers
 // alternate so that a TMEM load is always in flight behind the math; the loops stay rolled
 // (two inlined copies of the step body, one per buffer).
 __device__ __forceinline__ float ssq_row_fast(uint32_t tacc, uint32_t (&a)[16], uint32_t (&b)[16]) {
-  float ssq = 0.f;
+  unsigned long long ssq2 = pack2(0.f, 0.f);
   tmem_issue16(tacc, a);
 #pragma unroll 1
   for (int c = 0; c < 8; c += 2) {
     tmem_wait16(a); tmem_issue16(tacc + (c + 1) * 16, b);
-    ssq = ssq_chunk<16>(a, ssq);
+    ssq2 = ssq_chunk<16>(a, ssq2);
     tmem_wait16(b); tmem_issue16(tacc + ((c + 2) & 7) * 16, a);      // wraps to step 0 for the second sweep
-    ssq = ssq_chunk<16>(b, ssq);
+    ssq2 = ssq_chunk<16>(b, ssq2);
   }
-  return ssq;       // step 0 is in flight into `a`
+  float lo, hi;
+  unpack2(ssq2, lo, hi);
+  return lo + hi;   // step 0 is in flight into `a`
 }
 
 template <int BITS, bool LDS = false, bool LINEAR = false>
