@@ -397,27 +397,28 @@ __global__ void __launch_bounds__(kThreads, 1) k_decode_attn(DecodeParams P) {
 #pragma unroll
     for (int mb = 0; mb < 8; ++mb) acc[mb][0] = acc[mb][1] = acc[mb][2] = acc[mb][3] = 0.f;
     uint32_t w0[KW], w1[KW], n0[KW], n1[KW];
+    uint32_t vw[4][VW], vx[4][VW];                                   // value rows of this block and of the next
     uint32_t kn_bits = 0, kn_next = 0, vn_bits = 0, vn_next = 0;      // norms of keys gid (low half) and gid + 8 (high half)
-    auto fetch = [&](int64_t kb, uint32_t (&a0)[KW], uint32_t (&a1)[KW], uint32_t& kn, uint32_t& vn) {
+    // keys, value rows and norms of a block: fetched one block ahead of their use (fetching the value rows at the
+    // start of their own block left most of a memory latency exposed in every round)
+    auto fetch = [&](int64_t kb, uint32_t (&a0)[KW], uint32_t (&a1)[KW], uint32_t (&av)[4][VW], uint32_t& kn, uint32_t& vn) {
       const int64_t k_lo = kb + gid, k_hi = kb + 8 + gid;
       const int64_t c_lo = k_lo < s_end ? k_lo : s_begin, c_hi = k_hi < s_end ? k_hi : s_begin;
       load_quarter<KBITS>(keys + c_lo * GK, t, a0);
       load_quarter<KBITS>(keys + c_hi * GK, t, a1);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int64_t key = kb + 2 * t + (q & 1) + 8 * (q >> 1);         // keys 2t, 2t+1, 2t+8, 2t+9
+        load_eighth<VBITS>(vals + (key < s_end ? key : s_begin) * GV, gid, av[q]);
+      }
       kn = (uint32_t)__ldg(k_norms + c_lo) | ((uint32_t)__ldg(k_norms + c_hi) << 16);
       vn = (uint32_t)__ldg(v_norms + c_lo) | ((uint32_t)__ldg(v_norms + c_hi) << 16);
     };
     int64_t kb = s_begin + warp * 16;
-    if (kb < s_end) fetch(kb, w0, w1, kn_bits, vn_bits);
+    if (kb < s_end) fetch(kb, w0, w1, vw, kn_bits, vn_bits);
     for (; kb < s_end; kb += kWarps * 16) {
       const int64_t kn = kb + kWarps * 16;
-      if (kn < s_end) fetch(kn, n0, n1, kn_next, vn_next);
-      // the value rows of THIS block: in flight while the keys are scored
-      uint32_t vw[4][VW];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int64_t key = kb + 2 * t + (q & 1) + 8 * (q >> 1);         // keys 2t, 2t+1, 2t+8, 2t+9
-        load_eighth<VBITS>(vals + (key < s_end ? key : s_begin) * GV, gid, vw[q]);
-      }
+      if (kn < s_end) fetch(kn, n0, n1, vx, kn_next, vn_next);
       float c[4];
       score_block<KBITS>(w0, w1, bq, lutk, c);
       // logits of keys gid (c[0], c[1]) and gid + 8 (c[2], c[3]) for this lane's two rows
@@ -486,6 +487,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_decode_attn(DecodeParams P) {
       }
 #pragma unroll
       for (int k = 0; k < KW; ++k) { w0[k] = n0[k]; w1[k] = n1[k]; }
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int k = 0; k < VW; ++k) vw[q][k] = vx[q][k];
       kn_bits = kn_next; vn_bits = vn_next;
     }
     // ---- fold the warp: sums over the lanes that share (t & 1), pieces hi + lo two lanes apart
