@@ -1334,6 +1334,36 @@ int umma_prepare_rotation_image(const float* m, int D, void* image, cudaStream_t
   return check_launch();
 }
 
+// Prepared launch descriptions kept per thread: a few slots, least recently used one replaced.  A caller with static
+// buffers submits the same job arrays again and again (one plan, or a few plans in rotation as the host-streamed
+// cache does): a call whose array, device and switches match a slot only issues the kernel.
+constexpr int kLaunchSlots = 4;
+template <typename Batch>
+struct LaunchSlot {
+  Batch batch;
+  std::vector<unsigned char> jobs;
+  int dev = -1, ablate = 0, grid = 0;
+  unsigned long long stamp = 0;
+};
+template <typename Batch>
+static LaunchSlot<Batch>& pick_slot(LaunchSlot<Batch> (&slots)[kLaunchSlots], unsigned long long& clock, const void* jobs,
+                                    size_t job_bytes, int dev, int ablate, bool cacheable, bool& reuse) {
+  reuse = false;
+  int victim = 0;
+  for (int i = 0; i < kLaunchSlots; ++i) {
+    LaunchSlot<Batch>& s = slots[i];
+    if (cacheable && s.dev == dev && s.ablate == ablate && s.jobs.size() == job_bytes &&
+        memcmp(s.jobs.data(), jobs, job_bytes) == 0) {
+      reuse = true;
+      s.stamp = ++clock;
+      return s;
+    }
+    if (s.stamp < slots[victim].stamp) victim = i;
+  }
+  slots[victim].stamp = ++clock;
+  return slots[victim];
+}
+
 bool umma_quantize_eligible(const TqQuantizeJob& j) {
   if (force_simt()) return false;
   if (j.rotation_image == nullptr || j.D != kDim || j.normalize != 1 || j.idx_mode != TQ_IDX_PACKED) return false;
@@ -1353,17 +1383,20 @@ bool umma_quantize_eligible(const TqQuantizeJob& j) {
 int umma_quantize(const TqQuantizeJob* jobs, int n_jobs, cudaStream_t st) {
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return TQ_ELAUNCH;
-  static thread_local UmmaQuantBatch batch;      // large: keep it off the stack
-  // A caller with static buffers submits the same job array every step: the prepared launch
-  // description (tensor maps included) of this thread's previous call is reused when the
-  // array, the device and the switches are unchanged.  Per-thread, so calls stay re-entrant.
-  static thread_local std::vector<unsigned char> last_jobs;
-  static thread_local int last_dev = -1, last_ablate = 0, last_grid = 0;
+  // The prepared launch description (tensor maps included) of an earlier call of this thread is reused when the
+  // job array, the device and the switches are unchanged.  Per-thread, so calls stay re-entrant.
+  static thread_local LaunchSlot<UmmaQuantBatch> slots[kLaunchSlots];      // large: kept off the stack
+  static thread_local unsigned long long slot_clock = 0;
   int cur_dev = 0;
   cudaGetDevice(&cur_dev);
   const size_t job_bytes = (size_t)n_jobs * sizeof(TqQuantizeJob);
-  const bool reuse = n_jobs <= kMaxJobs && last_dev == cur_dev && last_ablate == ablate_flags() &&
-                     last_jobs.size() == job_bytes && memcmp(last_jobs.data(), jobs, job_bytes) == 0;
+  bool reuse = false;
+  LaunchSlot<UmmaQuantBatch>& slot = pick_slot(slots, slot_clock, jobs, job_bytes, cur_dev, ablate_flags(), n_jobs <= kMaxJobs, reuse);
+  UmmaQuantBatch& batch = slot.batch;
+  std::vector<unsigned char>& last_jobs = slot.jobs;
+  int& last_dev = slot.dev;
+  int& last_ablate = slot.ablate;
+  int& last_grid = slot.grid;
   last_dev = -1;                                 // invalid until this call has rebuilt or reused the batch
   int done = 0;
   while (done < n_jobs) {
@@ -1466,15 +1499,19 @@ bool umma_dequantize_eligible(const TqDequantizeJob& j) {
 int umma_dequantize(const TqDequantizeJob* jobs, int n_jobs, cudaStream_t st) {
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return TQ_ELAUNCH;
-  static thread_local UmmaDeqBatch batch;
-  // same reuse of the previous call's launch description as in umma_quantize
-  static thread_local std::vector<unsigned char> last_jobs;
-  static thread_local int last_dev = -1, last_ablate = 0, last_grid = 0;
+  // same reuse of earlier calls' launch descriptions as in umma_quantize
+  static thread_local LaunchSlot<UmmaDeqBatch> slots[kLaunchSlots];
+  static thread_local unsigned long long slot_clock = 0;
   int cur_dev = 0;
   cudaGetDevice(&cur_dev);
   const size_t job_bytes = (size_t)n_jobs * sizeof(TqDequantizeJob);
-  const bool reuse = n_jobs <= kMaxDeqJobs && last_dev == cur_dev && last_ablate == ablate_flags() &&
-                     last_jobs.size() == job_bytes && memcmp(last_jobs.data(), jobs, job_bytes) == 0;
+  bool reuse = false;
+  LaunchSlot<UmmaDeqBatch>& slot = pick_slot(slots, slot_clock, jobs, job_bytes, cur_dev, ablate_flags(), n_jobs <= kMaxDeqJobs, reuse);
+  UmmaDeqBatch& batch = slot.batch;
+  std::vector<unsigned char>& last_jobs = slot.jobs;
+  int& last_dev = slot.dev;
+  int& last_ablate = slot.ablate;
+  int& last_grid = slot.grid;
   last_dev = -1;
   int done = 0;
   while (done < n_jobs) {

@@ -180,7 +180,8 @@ class CachePlan:
 
         The plan's buffers and job arrays are static.  When the whole plan goes out as ONE tensor-core launch
         per call (every job eligible, one input dtype, at most 96 jobs) the library keeps the prepared launch
-        description of its previous call and the captured call only issues the kernel; a plan that splits into
+        descriptions of the last four distinct job arrays of the calling thread and the captured call only issues
+        the kernel; a plan that splits into
         several launches re-encodes its tensor maps on every call, which stream capture tolerates but which
         costs host time.  One eager pass runs first."""
         side = torch.cuda.Stream(self.device)
