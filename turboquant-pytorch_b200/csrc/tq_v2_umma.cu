@@ -41,9 +41,14 @@ template <int D>
 struct VCfg {
   static constexpr int KC = D / 64;            // k chunks
   static constexpr int NBLK = D / 128;         // blocks of 128 output columns
-  static constexpr uint32_t kOffA = 0;                                   // [piece 2][kc] chunks
-  static constexpr uint32_t kOffB = kOffA + 2u * KC * kChunk;            // ring
-  static constexpr uint32_t kOffTab = kOffB + kNB * kChunk;              // thresholds, centroid piece pairs, cell table, partial sums
+  // A: two k-chunk slots per piece (chunk kc lands in slot kc & 1 and is released as soon as its MMAs are done), so
+  // that the B ring can hold stages of ALL output columns: one MMA of N = D per k-step instead of one per block of
+  // 128 columns (an MMA takes ~127 clocks whatever its N, so N = 256 halves the tensor time at head_dim 256)
+  static constexpr int kASlots = 2;
+  static constexpr uint32_t kBStage = NBLK * kChunk;                     // one k-chunk of B for all D output columns
+  static constexpr uint32_t kOffA = 0;                                   // [piece 2][slot 2] chunks
+  static constexpr uint32_t kOffB = kOffA + 2u * kASlots * kChunk;       // ring
+  static constexpr uint32_t kOffTab = kOffB + kNB * kBStage;             // thresholds, centroid piece pairs, cell table, partial sums
   static constexpr uint32_t kOffBar = kOffTab + 6144;
   static constexpr int kThreads = 64 + 2 * NBLK * 128;                   // two tiles in flight, one warpgroup per 128 columns
   static constexpr uint32_t kUsedBytes = kOffBar + 256;
@@ -130,8 +135,8 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
   uint8_t* cells_s = gbase + C::kOffTab + 2048;                        // 1028 bytes
   float* part_s = reinterpret_cast<float*>(gbase + C::kOffTab + 4096); // [slot 2][row 128] partial sums of the upper block
   const uint32_t bar0 = base + C::kOffBar;
-  const uint32_t bar_afull = bar0;                          // [KC] TMA -> MMA (all pieces of a k-chunk)
-  const uint32_t bar_aempty = bar_afull + 8 * 4;            // [KC] MMA commit -> producer
+  const uint32_t bar_afull = bar0;                          // [kASlots] TMA -> MMA (all pieces of a k-chunk)
+  const uint32_t bar_aempty = bar_afull + 8 * 4;            // [kASlots] MMA commit -> producer
   const uint32_t bar_bfull = bar_aempty + 8 * 4;            // [kNB] bulk copy -> MMA
   const uint32_t bar_bempty = bar_bfull + 8 * kNB;          // [kNB] MMA commit -> producer
   const uint32_t bar_tfull = bar_bempty + 8 * kNB;          // [2] MMA commit -> epilogue
@@ -146,7 +151,7 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
   const int n_local = t1 - t0;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < KC; ++i) { mbar_init(bar_afull + 8 * i, 1); mbar_init(bar_aempty + 8 * i, 1); }
+    for (int i = 0; i < C::kASlots; ++i) { mbar_init(bar_afull + 8 * i, 1); mbar_init(bar_aempty + 8 * i, 1); }
     for (int i = 0; i < kNB; ++i) { mbar_init(bar_bfull + 8 * i, 1); mbar_init(bar_bempty + 8 * i, 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, 4 * NBLK); }
     *abort_flag = 0;
@@ -174,23 +179,23 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
     if (lane == 0) {
       bool ok = true;
       int bc = 0;                                           // running B chunk counter
+      int ac = 0;                                           // running A chunk counter: slot ac & 1, use ac / 2
       for (int i = 0; i < n_local && ok; ++i) {
         const int row0 = (t0 + i) * kRowsT;
-        for (int kc = 0; kc < KC && ok; ++kc) {
-          ok = mbar_wait(bar_aempty + 8 * kc, (uint32_t)((i & 1) ^ 1), abort_flag);
+        for (int kc = 0; kc < KC && ok; ++kc, ++ac) {
+          const int as = ac % C::kASlots;
+          ok = mbar_wait(bar_aempty + 8 * as, (uint32_t)(((ac / C::kASlots) & 1) ^ 1), abort_flag);
           if (!ok) break;
-          mbar_arrive_expect_tx(bar_afull + 8 * kc, PA * kChunk);
-          tma_load_2d(a_smem + kc * kChunk, &p.a_hi_map, kc * 64, row0, bar_afull + 8 * kc);
-          if constexpr (PA == 2) tma_load_2d(a_smem + (KC + kc) * kChunk, &p.a_lo_map, kc * 64, row0, bar_afull + 8 * kc);
-          for (int nb = 0; nb < NBLK && ok; ++nb) {
-            for (int pb = 0; pb < 2; ++pb) {
-              const int s = bc % kNB;
-              ok = mbar_wait(bar_bempty + 8 * s, (uint32_t)(((bc / kNB) & 1) ^ 1), abort_flag);
-              if (!ok) break;
-              mbar_arrive_expect_tx(bar_bfull + 8 * s, kChunk);
-              bulk_load(b_smem + s * kChunk, p.b_image + ((size_t)(pb * KC + kc) * NBLK + nb) * kChunk, kChunk, bar_bfull + 8 * s);
-              ++bc;
-            }
+          mbar_arrive_expect_tx(bar_afull + 8 * as, PA * kChunk);
+          tma_load_2d(a_smem + as * kChunk, &p.a_hi_map, kc * 64, row0, bar_afull + 8 * as);
+          if constexpr (PA == 2) tma_load_2d(a_smem + (C::kASlots + as) * kChunk, &p.a_lo_map, kc * 64, row0, bar_afull + 8 * as);
+          for (int pb = 0; pb < 2; ++pb) {
+            const int s = bc % kNB;
+            ok = mbar_wait(bar_bempty + 8 * s, (uint32_t)(((bc / kNB) & 1) ^ 1), abort_flag);
+            if (!ok) break;
+            mbar_arrive_expect_tx(bar_bfull + 8 * s, C::kBStage);
+            bulk_load(b_smem + s * C::kBStage, p.b_image + (size_t)(pb * KC + kc) * C::kBStage, C::kBStage, bar_bfull + 8 * s);
+            ++bc;
           }
         }
       }
@@ -199,8 +204,10 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
         if (p.status != nullptr) atomicCAS(p.status, 0, (STAGE << 20) | (1 << 16) | (int)blockIdx.x);
       }
       // none of this CTA's own copies may still be in flight when it exits
-      if (n_local > 0)
-        for (int kc = 0; kc < KC; ++kc) mbar_wait(bar_afull + 8 * kc, (uint32_t)((n_local - 1) & 1), abort_flag);
+      for (int k = 0; k < C::kASlots && k < ac; ++k) {
+        const int j = ac - 1 - k;
+        mbar_wait(bar_afull + 8 * (j % C::kASlots), (uint32_t)((j / C::kASlots) & 1), abort_flag);
+      }
       for (int k = 0; k < kNB && k < bc; ++k) {
         const int j = bc - 1 - k;
         mbar_wait(bar_bfull + 8 * (j % kNB), (uint32_t)((j / kNB) & 1), abort_flag);
@@ -210,22 +217,24 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
     // ------------------------------------------------------------ MMA issuer (converged warp, one elected lane issues)
     bool ok = true;
     int bc = 0;
-    const uint32_t idesc = idesc_f16(false);                // M = 128, N = 128, fp16
+    // M = 128, N = D (all output columns in one instruction: rows 128.. of the B stage are the second block), fp16
+    const uint32_t idesc = (idesc_f16(false) & ~(0x3Fu << 17)) | ((uint32_t)(D >> 3) << 17);
+    int ac = 0;
     for (int i = 0; i < n_local && ok; ++i) {
       const int slot = i & 1;
       ok = mbar_wait(bar_tempty + 8 * slot, (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
 #pragma unroll 1
-      for (int kc = 0; kc < KC && ok; ++kc) {
-        ok = mbar_wait(bar_afull + 8 * kc, (uint32_t)(i & 1), abort_flag);
+      for (int kc = 0; kc < KC && ok; ++kc, ++ac) {
+        const int as = ac % C::kASlots;
+        ok = mbar_wait(bar_afull + 8 * as, (uint32_t)((ac / C::kASlots) & 1), abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        const uint64_t a_hi = smem_desc_sw128(a_smem + kc * kChunk);
-        const uint64_t a_lo = smem_desc_sw128(a_smem + (KC + kc) * kChunk);
-#pragma unroll 1
-        for (int nb = 0; nb < NBLK && ok; ++nb) {
-          const uint32_t d_tmem = tmem_base + (uint32_t)(slot * NBLK * 128 + nb * 128);
+        const uint64_t a_hi = smem_desc_sw128(a_smem + as * kChunk);
+        const uint64_t a_lo = smem_desc_sw128(a_smem + (C::kASlots + as) * kChunk);
+        {
+          const uint32_t d_tmem = tmem_base + (uint32_t)(slot * NBLK * 128);
 #pragma unroll 1
           for (int pb = 0; pb < 2; ++pb) {
             const int s = bc % kNB;
@@ -233,7 +242,7 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const uint64_t b_desc = smem_desc_sw128(b_smem + s * kChunk);
+            const uint64_t b_desc = smem_desc_sw128(b_smem + s * C::kBStage);
             if (elect_one()) {
               if (pb == 0) {
 #pragma unroll
@@ -247,8 +256,8 @@ __global__ void __launch_bounds__(VCfg<D>::kThreads, 1) k_umma_v2_stage(const __
                 for (int k = 0; k < 4; ++k) umma_f16(d_tmem, a_hi + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, 1u);
               }
               umma_commit(bar_bempty + 8 * s);              // the ring stage is free once these MMAs are done
-              if (nb == NBLK - 1 && pb == 1) {
-                umma_commit(bar_aempty + 8 * kc);           // last use of this k-chunk of A
+              if (pb == 1) {
+                umma_commit(bar_aempty + 8 * as);           // last use of this k-chunk of A
                 if (kc == KC - 1) umma_commit(bar_tfull + 8 * slot);
               }
             }
