@@ -185,3 +185,27 @@ def test_tensor_core_dequantize_many_layers_one_launch():
     for l in range(L):
         for got, ref in zip(outs[l], refs[l]):
             assert float((got.float() - ref.float()).abs().max()) <= 2e-3 * float(ref.float().abs().max())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits", [2, 4, 6, 8])
+def test_index_rows_at_a_16_byte_offset_equal_the_aligned_ones(bits):
+    """The tensor-core quantiser writes 32 bytes per store when a row allows it; a destination that is only 16-byte
+    aligned takes the narrower stores and must give the same bytes (and nothing outside its rows)."""
+    import turboquant as tq
+    from turboquant import _native as N, _ops
+    x = O.synthetic_kv((1, 2, 300, 128), torch.bfloat16, seed=81000 + bits).to("cuda:0")
+    comp = tq.MSECompressor(128, bits, seed=5, device="cuda:0")
+    job, res, _keep = comp.compress_job(x)
+    _ops.run_quantize([job], x.device)
+    want = res["idx_bytes"].clone()
+    g = want.shape[-1]
+    raw = torch.full((want.numel() + 64,), 0xA5, dtype=torch.uint8, device=x.device)
+    assert raw.data_ptr() % 32 == 0
+    job.idx_out = raw.data_ptr() + 16
+    _ops.run_quantize([job], x.device)
+    torch.cuda.synchronize()
+    got = raw[16:16 + want.numel()].reshape(want.shape)
+    assert torch.equal(got, want)
+    assert bool((raw[:16] == 0xA5).all()) and bool((raw[16 + want.numel():] == 0xA5).all())
+    assert g == N.packed_row_bytes(128, bits) and N.lib().tq_last_device_status() == 0
