@@ -1293,15 +1293,17 @@ void partition_tiles(const int64_t* tiles, const int* weight, int n_jobs, int gr
   cta_begin[grid] = (int32_t)total_tiles;
 }
 
-// Cost of a 128-vector tile per code width, in units of 10 ns on one SM at full clocks (measured on
-// (8, 8, 32768, 128) tensors, one width at a time); only the ratios matter.
+// Cost of a 128-vector tile per code width, in units of about 10 ns on one SM; only the ratios matter.  Measured
+// on (8, 8, 32768, 128) tensors one width at a time, then corrected with the per-CTA times of a mixed launch
+// (K6/V4 layers with 8-bit protected layers, all widths running side by side under the power cap), where the
+// CTAs of the 8-bit jobs finished 6 % after the average and those of the 4-bit jobs 5 % before it.
 int quantize_tile_weight(int bits, bool bf16) {
-  if (bf16) return bits <= 2 ? 140 : bits <= 5 ? 152 : bits == 6 ? 170 : 207;
+  if (bf16) return bits <= 2 ? 133 : bits <= 5 ? 144 : bits == 6 ? 170 : 219;
   return bits <= 2 ? 117 : bits <= 4 ? 137 : bits == 5 ? 146 : bits == 6 ? 163 : 203;
 }
 int dequantize_tile_weight(int bits, bool out32) {
   if (out32) return bits <= 4 ? 250 : 300;
-  return bits <= 2 ? 127 : bits <= 4 ? 131 : bits <= 7 ? 146 : 163;
+  return bits <= 2 ? 127 : bits <= 4 ? 130 : bits <= 7 ? 152 : 157;
 }
 
 }  // namespace
