@@ -88,9 +88,11 @@ def synthetic_layer(cfg, layer: int, kv: int, heads, device):
 
 
 def rank_layers(cfg, rank: int, world: int):
-    """[(layer, range of KV heads)] owned by `rank`: contiguous blocks of the layer-major (layer, head) units."""
+    """[(layer, range of KV heads)] owned by `rank`: contiguous blocks of the layer-major (layer, head) units, of
+    equal estimated cost (the 8-bit protected layers cost more per vector than the K6/V4 ones)."""
     from turboquant import batched
-    units = batched.shard_units(cfg["layers"], cfg["kv_heads"], rank, world)
+    costs = [batched.tile_cost(*layer_bits(cfg, l)) for l in range(cfg["layers"])]
+    units = batched.shard_units(cfg["layers"], cfg["kv_heads"], rank, world, layer_costs=costs)
     out = []
     for layer, head in units:
         if out and out[-1][0] == layer:
@@ -758,7 +760,7 @@ def main():
         "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16xbf16->f32" if cfg["dtype"] == torch.bfloat16 else "f16xf16->f32", "data": "synthetic",
         "config": {"workload": cfg["name"] + (" [reduced for profiling]" if reduced else ""),
-                   "partition": f"{cfg['layers'] * cfg['kv_heads']} (layer, KV head) units in contiguous blocks over "
+                   "partition": f"{cfg['layers'] * cfg['kv_heads']} (layer, KV head) units in contiguous blocks of equal estimated cost over "
                                 f"{world} rank(s), no collective on the data path",
                    "rank0_layers": len(layers), "vectors_per_step": int(vectors_all),
                    "l2": "a 256 MiB buffer is overwritten before each phase (outside the event-timed intervals); "

@@ -92,3 +92,23 @@ def test_rank_blocks_cover_the_cache_for_every_world_size():
                     assert heads.step == 1 and 0 <= heads.start < heads.stop <= cfg["kv_heads"]
                     seen += [(layer, h) for h in heads]
             assert sorted(seen) == [(l, h) for l in range(cfg["layers"]) for h in range(cfg["kv_heads"])]
+
+
+def test_cost_balanced_shards_cover_the_units_and_equalise_the_cost():
+    import sys
+    sys.path.insert(0, os.path.join(ROOT, "turboquant-pytorch_b200"))
+    from turboquant import batched
+    layers, heads = 32, 8
+    costs = [batched.tile_cost(8, 8) if l < 4 or l >= 28 else batched.tile_cost(6, 4) for l in range(layers)]
+    assert batched.tile_cost(8, 8) > batched.tile_cost(6, 4) > batched.tile_cost(4, 2)
+    for world in (1, 2, 3, 4, 8, 16):
+        shards = [batched.shard_units(layers, heads, r, world, layer_costs=costs) for r in range(world)]
+        flat = [u for sh in shards for u in sh]
+        assert flat == [(l, h) for l in range(layers) for h in range(heads)]          # contiguous, complete, in order
+        load = [sum(costs[l] for l, _h in sh) for sh in shards]
+        assert max(load) - min(load) <= 1.5 * max(costs)                               # within a unit and a half
+        plain = [len(batched.shard_units(layers, heads, r, world)) for r in range(world)]
+        assert sum(plain) == layers * heads and max(plain) - min(plain) <= 1
+    # the protected layers make the end shards shorter
+    eight = [len(batched.shard_units(layers, heads, r, 8, layer_costs=costs)) for r in range(8)]
+    assert eight[0] < 32 < eight[3] and eight[0] == eight[-1]

@@ -277,14 +277,40 @@ class HostStreamedCache:
         return self.host_out_keys, self.host_out_values
 
 
-def shard_units(n_layers: int, n_kv_heads: int, rank: int, world: int):
+def shard_units(n_layers: int, n_kv_heads: int, rank: int, world: int, layer_costs=None):
     """(layer, kv_head) units owned by `rank`: contiguous blocks of the layer-major unit list.
 
     Units are independent (no collective on the data path); a contiguous block
     keeps each rank's layers adjacent, so it needs the constants of as few layers
-    as possible.
+    as possible.  With layer_costs (one relative cost per layer, e.g. from tile_cost()) the blocks have equal
+    cost instead of equal length: the 8-bit protected layers at both ends of a cache cost ~1.25 x an ordinary
+    K6/V4 layer, and with equal lengths the first and the last rank finish last.
     """
     total = n_layers * n_kv_heads
-    lo = total * rank // world
-    hi = total * (rank + 1) // world
+    if layer_costs is None:
+        lo = total * rank // world
+        hi = total * (rank + 1) // world
+    else:
+        if len(layer_costs) != n_layers or min(layer_costs) <= 0:
+            raise ValueError("layer_costs: one positive number per layer")
+        cum = [0.0]
+        for u in range(total):
+            cum.append(cum[-1] + float(layer_costs[u // n_kv_heads]))
+        bounds = [0]
+        for r in range(1, world):
+            target = cum[-1] * r / world
+            b = bounds[-1]
+            while b < total and abs(cum[b + 1] - target) <= abs(cum[b] - target):
+                b += 1
+            bounds.append(b)
+        bounds.append(total)
+        lo, hi = bounds[rank], bounds[rank + 1]
     return [(u // n_kv_heads, u % n_kv_heads) for u in range(lo, hi)]
+
+
+def tile_cost(key_bits: int, value_bits: int) -> float:
+    """Relative cost of quantising and dequantising one K and one V vector at these widths on the tensor-core path
+    (bf16 tile weights of the library, measured on B200): for cost-balanced shards."""
+    q = {1: 133, 2: 133, 3: 144, 4: 144, 5: 144, 6: 170, 7: 219, 8: 219}
+    d = {1: 127, 2: 127, 3: 130, 4: 130, 5: 152, 6: 152, 7: 152, 8: 157}
+    return float(q[key_bits] + q[value_bits] + d[key_bits] + d[value_bits])
